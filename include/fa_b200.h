@@ -1,0 +1,104 @@
+/*
+ * fa_b200.h -- C ABI of libfa_b200.so: FlashAttention forward for NVIDIA B200 (sm_100a).
+ *
+ * This is the boundary a foreign-function binding (ctypes, pybind11, cgo ...) binds to.
+ * It replaces the host launcher of the reference project,
+ *
+ *   template <typename T> cudaError_t flashattention_forward(T* O, const T* Q, const T* K,
+ *       const T* V, int seq_len, int batch_size, int num_heads);
+ *   (reference: src/cpp/v1.cu:4-38, declared again in src/cpp/torch_bind.cpp:9-11)
+ *
+ * which the reference's torch extension `custom_flash_attn.forward(Q, K, V)` calls
+ * (reference: src/cpp/torch_bind.cpp:21-49).  Differences that a caller sees:
+ *   - plain C symbols, plain pointers and sizes, no torch types, no exceptions;
+ *   - explicit device and stream instead of device 0 / the legacy default stream;
+ *   - explicit element strides (the innermost stride is always 1);
+ *   - a `causal` flag (the reference is always causal) and an optional LSE output;
+ *   - the error code is returned and has a message (the reference drops it).
+ *
+ * Conventions
+ *   - q, k, v, o are bf16 device pointers addressing logical [B, H, N, d] tensors, d == 64.
+ *   - strides are in ELEMENTS, order {batch, head, row}; each must be a multiple of 8
+ *     (16 bytes) and the base pointers must be 16-byte aligned.
+ *   - lse, when not NULL, is a contiguous fp32 [B, H, N] device buffer that receives
+ *     logsumexp_j(softmax_scale * q_i . k_j) in natural-log units.
+ *   - return value: 0 = kernel enqueued; < 0 = argument error, no CUDA call was made;
+ *     > 0 = a cudaError_t from the CUDA runtime.
+ *   - all entry points are thread-safe; calls on different devices do not share state.
+ */
+#ifndef FA_B200_H_
+#define FA_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FA_B200_ABI_VERSION 1
+
+/* argument errors (negative return values) */
+#define FA_B200_OK                 0
+#define FA_B200_ERR_NULL          -1  /* params, q, k, v or o is NULL                      */
+#define FA_B200_ERR_HEAD_DIM      -2  /* d != 64                                           */
+#define FA_B200_ERR_SHAPE         -3  /* B, H or N negative, or too large for the kernel   */
+#define FA_B200_ERR_STRIDE        -4  /* a stride is <= 0 or not a multiple of 8 elements  */
+#define FA_B200_ERR_ALIGN         -5  /* a base pointer is not 16-byte aligned             */
+#define FA_B200_ERR_SCALE         -6  /* softmax_scale is NaN, infinite or negative        */
+#define FA_B200_ERR_DEVICE        -7  /* device index negative                             */
+#define FA_B200_ERR_ARCH          -8  /* device is not compute capability 10.x             */
+#define FA_B200_ERR_TENSORMAP     -9  /* the driver refused a TMA descriptor               */
+#define FA_B200_ERR_DRIVER       -10  /* cuTensorMapEncodeTiled could not be resolved      */
+
+typedef struct fa_b200_params {
+  const void* q;            /* bf16 [B,H,N,d] */
+  const void* k;            /* bf16 [B,H,N,d] */
+  const void* v;            /* bf16 [B,H,N,d] */
+  void*       o;            /* bf16 [B,H,N,d], written */
+  float*      lse;          /* fp32 [B,H,N] contiguous, written; may be NULL */
+  int32_t     B, H, N, d;   /* d must be 64 */
+  int64_t     q_strides[3]; /* elements: {batch, head, row} */
+  int64_t     k_strides[3];
+  int64_t     v_strides[3];
+  int64_t     o_strides[3];
+  float       softmax_scale; /* 0 selects 1/sqrt(d), the reference's fixed scale (v1.cu:17) */
+  int32_t     causal;        /* non-zero: row i attends columns j <= i (the reference's only mode,
+                                v1_implementation.hpp:108-112); zero: full attention */
+  int32_t     device;        /* CUDA device ordinal that owns all pointers */
+  void*       stream;        /* cudaStream_t; NULL = that device's default stream */
+} fa_b200_params;
+
+/* Enqueue one attention forward on p->stream.  Asynchronous: returns once the kernel is
+ * launched, like the reference launcher (v1.cu:29-37).  Replaces flashattention_forward<T>
+ * (reference src/cpp/v1.cu:4-38). */
+int fa_b200_fwd(const fa_b200_params* p);
+
+/* Check arguments exactly as fa_b200_fwd does, without touching CUDA.  Returns 0 or a negative
+ * FA_B200_ERR_* code.  Covers what CHECK_INPUT and the dtype branch police in the reference
+ * binding (src/cpp/torch_bind.cpp:13-19, 33-42), plus what it leaves unchecked (size(3)). */
+int fa_b200_validate(const fa_b200_params* p);
+
+/* Message for a value returned by any function here (negative: argument error, positive:
+ * cudaGetErrorString).  The returned pointer stays valid for the life of the process. */
+const char* fa_b200_strerror(int code);
+
+/* 1 if `device` exists and is compute capability 10.x, 0 if it exists and is not, negative /
+ * positive error otherwise.  The reference has no such check (it queries device 0 on every
+ * call, src/cpp/v1.cu:7-8). */
+int fa_b200_device_ok(int device);
+
+/* Synchronise `stream` on `device`, then return and clear the device-side watchdog word.
+ * Every wait inside the kernel is bounded; a wait that runs out records which one it was and
+ * the kernel drains and exits.  0 = all kernels since the last call finished normally;
+ * > 0x10000 = watchdog code (see fa_b200_strerror); other values = cudaError_t.
+ * The reference has no counterpart (its cudaGetLastError result is dropped,
+ * src/cpp/torch_bind.cpp:34-39). */
+int fa_b200_last_status(int device, void* stream);
+
+/* FA_B200_ABI_VERSION the library was built with. */
+int fa_b200_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA_B200_H_ */

@@ -1,0 +1,65 @@
+"""ctypes binding of libfa_b200.so -- the declarations in include/fa_b200.h, one to one.
+
+There is no fallback: if the library is missing, or the device is not a B200, calls raise.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libfa_b200.so")
+
+ABI_VERSION = 1
+
+
+class FaParams(ctypes.Structure):
+    """struct fa_b200_params (include/fa_b200.h)."""
+    _fields_ = [
+        ("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p),
+        ("o", ctypes.c_void_p), ("lse", ctypes.c_void_p),
+        ("B", ctypes.c_int32), ("H", ctypes.c_int32), ("N", ctypes.c_int32), ("d", ctypes.c_int32),
+        ("q_strides", ctypes.c_int64 * 3), ("k_strides", ctypes.c_int64 * 3),
+        ("v_strides", ctypes.c_int64 * 3), ("o_strides", ctypes.c_int64 * 3),
+        ("softmax_scale", ctypes.c_float), ("causal", ctypes.c_int32),
+        ("device", ctypes.c_int32), ("stream", ctypes.c_void_p),
+    ]
+
+
+EXPORTS = ("fa_b200_fwd", "fa_b200_validate", "fa_b200_strerror", "fa_b200_device_ok",
+           "fa_b200_last_status", "fa_b200_abi_version")
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the library once and declare every exported symbol's signature."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m tfg_flashattention_b200.build` "
+            "(needs nvcc; there is no CPU or PyTorch fallback for this kernel)")
+    lib = ctypes.CDLL(LIB_PATH)
+    P = ctypes.POINTER(FaParams)
+    lib.fa_b200_fwd.argtypes = [P]
+    lib.fa_b200_fwd.restype = ctypes.c_int
+    lib.fa_b200_validate.argtypes = [P]
+    lib.fa_b200_validate.restype = ctypes.c_int
+    lib.fa_b200_strerror.argtypes = [ctypes.c_int]
+    lib.fa_b200_strerror.restype = ctypes.c_char_p
+    lib.fa_b200_device_ok.argtypes = [ctypes.c_int]
+    lib.fa_b200_device_ok.restype = ctypes.c_int
+    lib.fa_b200_last_status.argtypes = [ctypes.c_int, ctypes.c_void_p]
+    lib.fa_b200_last_status.restype = ctypes.c_int
+    lib.fa_b200_abi_version.argtypes = []
+    lib.fa_b200_abi_version.restype = ctypes.c_int
+    if lib.fa_b200_abi_version() != ABI_VERSION:
+        raise RuntimeError("libfa_b200.so was built from a different include/fa_b200.h; rebuild it")
+    _lib = lib
+    return lib
+
+
+def strerror(code: int) -> str:
+    return load().fa_b200_strerror(code).decode()

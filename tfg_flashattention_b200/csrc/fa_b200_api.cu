@@ -1,0 +1,234 @@
+// Host side of libfa_b200.so: the C ABI declared in include/fa_b200.h.
+// Validates arguments, builds the TMA descriptors, launches the sm_100a kernel on the caller's
+// stream.  No exceptions, no torch types, no CPU fallback: a device that is not 10.x is an error.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+
+#include "../../include/fa_b200.h"
+#include "fa_fwd_sm100.cuh"
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct DeviceState {
+  std::once_flag once;
+  int init_error = 0;       // value fa_b200_fwd returns if set-up failed
+  unsigned int* status = nullptr;  // device address of the watchdog words
+};
+
+DeviceState g_dev[kMaxDevices];
+std::once_flag g_encode_once;
+EncodeTiledFn g_encode = nullptr;
+
+// Watchdog words, one set per device that loads the module (a __device__ variable is
+// instantiated per device).  Word 0: code, 1: blockIdx.x, 2: threadIdx.x, 3: barrier parity.
+__device__ unsigned int g_fa_status[4];
+
+void resolve_encode() {
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) ==
+          cudaSuccess &&
+      qres == cudaDriverEntryPointSuccess)
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+}
+
+struct DeviceGuard {
+  int prev = -1;
+  bool switched = false;
+  int error = 0;
+  explicit DeviceGuard(int dev) {
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) { error = static_cast<int>(e); return; }
+    if (prev != dev) {
+      e = cudaSetDevice(dev);
+      if (e != cudaSuccess) { error = static_cast<int>(e); return; }
+      switched = true;
+    }
+  }
+  ~DeviceGuard() {
+    if (switched) cudaSetDevice(prev);
+  }
+};
+
+// Runs once per device, with that device current.
+void init_device(int dev) {
+  DeviceState& st = g_dev[dev];
+  cudaDeviceProp prop;
+  cudaError_t e = cudaGetDeviceProperties(&prop, dev);
+  if (e != cudaSuccess) { st.init_error = static_cast<int>(e); return; }
+  if (prop.major != 10) { st.init_error = FA_B200_ERR_ARCH; return; }
+  e = cudaFuncSetAttribute(fa::fa_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           fa::kSmemBytes);
+  if (e != cudaSuccess) { st.init_error = static_cast<int>(e); return; }
+  void* addr = nullptr;
+  e = cudaGetSymbolAddress(&addr, g_fa_status);
+  if (e != cudaSuccess) { st.init_error = static_cast<int>(e); return; }
+  st.status = static_cast<unsigned int*>(addr);
+  e = cudaMemset(st.status, 0, 4 * sizeof(unsigned int));
+  if (e != cudaSuccess) { st.init_error = static_cast<int>(e); return; }
+}
+
+bool stride_ok(const int64_t s[3]) {
+  for (int i = 0; i < 3; ++i)
+    if (s[i] <= 0 || (s[i] % 8) != 0) return false;
+  return true;
+}
+
+int encode_map(CUtensorMap* map, const void* base, const fa_b200_params* p, const int64_t st[3]) {
+  // dims, innermost first: d, N, H, B.  Strides (bytes) for dims 1..3: row, head, batch.
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(p->d), static_cast<cuuint64_t>(p->N),
+                              static_cast<cuuint64_t>(p->H), static_cast<cuuint64_t>(p->B)};
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(st[2]) * 2, static_cast<cuuint64_t>(st[1]) * 2,
+                                 static_cast<cuuint64_t>(st[0]) * 2};
+  const cuuint32_t box[4] = {fa::kHeadDim, fa::kBlockN, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : FA_B200_ERR_TENSORMAP;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fa_b200_abi_version(void) { return FA_B200_ABI_VERSION; }
+
+int fa_b200_validate(const fa_b200_params* p) {
+  if (p == nullptr || p->q == nullptr || p->k == nullptr || p->v == nullptr || p->o == nullptr)
+    return FA_B200_ERR_NULL;
+  if (p->d != fa::kHeadDim) return FA_B200_ERR_HEAD_DIM;
+  if (p->B < 0 || p->H < 0 || p->N < 0) return FA_B200_ERR_SHAPE;
+  if (p->N > (1 << 24)) return FA_B200_ERR_SHAPE;
+  {
+    const long long ctas = static_cast<long long>(p->B) * p->H * ((p->N + 255) / 256);
+    if (ctas > 0x7fffffffLL) return FA_B200_ERR_SHAPE;
+  }
+  if (!stride_ok(p->q_strides) || !stride_ok(p->k_strides) || !stride_ok(p->v_strides) ||
+      !stride_ok(p->o_strides))
+    return FA_B200_ERR_STRIDE;
+  const uintptr_t ptrs[4] = {reinterpret_cast<uintptr_t>(p->q), reinterpret_cast<uintptr_t>(p->k),
+                             reinterpret_cast<uintptr_t>(p->v), reinterpret_cast<uintptr_t>(p->o)};
+  for (uintptr_t a : ptrs)
+    if (a & 15u) return FA_B200_ERR_ALIGN;
+  if (p->lse != nullptr && (reinterpret_cast<uintptr_t>(p->lse) & 3u)) return FA_B200_ERR_ALIGN;
+  if (!(p->softmax_scale >= 0.0f) || std::isinf(p->softmax_scale)) return FA_B200_ERR_SCALE;
+  if (p->device < 0 || p->device >= kMaxDevices) return FA_B200_ERR_DEVICE;
+  return FA_B200_OK;
+}
+
+int fa_b200_fwd(const fa_b200_params* p) {
+  int rc = fa_b200_validate(p);
+  if (rc != FA_B200_OK) return rc;
+  if (p->B == 0 || p->H == 0 || p->N == 0) return FA_B200_OK;  // nothing to compute
+
+  DeviceGuard guard(p->device);
+  if (guard.error) return guard.error;
+  DeviceState& st = g_dev[p->device];
+  std::call_once(st.once, init_device, p->device);
+  if (st.init_error) return st.init_error;
+  std::call_once(g_encode_once, resolve_encode);
+  if (g_encode == nullptr) return FA_B200_ERR_DRIVER;
+
+  CUtensorMap mq, mk, mv;
+  if ((rc = encode_map(&mq, p->q, p, p->q_strides)) != 0) return rc;
+  if ((rc = encode_map(&mk, p->k, p, p->k_strides)) != 0) return rc;
+  if ((rc = encode_map(&mv, p->v, p, p->v_strides)) != 0) return rc;
+
+  fa::FwdParams kp;
+  kp.o = static_cast<__nv_bfloat16*>(p->o);
+  kp.lse = p->lse;
+  kp.o_sb = p->o_strides[0];
+  kp.o_sh = p->o_strides[1];
+  kp.o_sn = p->o_strides[2];
+  kp.B = p->B;
+  kp.H = p->H;
+  kp.N = p->N;
+  kp.n_pairs = (p->N + 2 * fa::kBlockM - 1) / (2 * fa::kBlockM);
+  kp.causal = p->causal ? 1 : 0;
+  const float scale = p->softmax_scale > 0.0f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(p->d));
+  kp.scale_log2 = scale * 1.4426950408889634f;
+  kp.status = st.status;
+
+  const unsigned grid = static_cast<unsigned>(static_cast<long long>(p->B) * p->H * kp.n_pairs);
+  fa::fa_fwd_kernel<<<grid, fa::kNumThreads, fa::kSmemBytes, static_cast<cudaStream_t>(p->stream)>>>(
+      mq, mk, mv, kp);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int fa_b200_device_ok(int device) {
+  if (device < 0) return FA_B200_ERR_DEVICE;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (device >= count) return FA_B200_ERR_DEVICE;
+  int major = 0;
+  e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return major == 10 ? 1 : 0;
+}
+
+int fa_b200_last_status(int device, void* stream) {
+  if (device < 0 || device >= kMaxDevices) return FA_B200_ERR_DEVICE;
+  DeviceGuard guard(device);
+  if (guard.error) return guard.error;
+  cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  DeviceState& st = g_dev[device];
+  if (st.status == nullptr) return 0;  // no kernel was ever launched on this device
+  unsigned int words[4] = {0, 0, 0, 0};
+  e = cudaMemcpy(words, st.status, sizeof(words), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (words[0] != 0) {
+    std::fprintf(stderr, "fa_b200: watchdog code 0x%x (block %u, thread %u, parity %u)\n", words[0],
+                 words[1], words[2], words[3]);
+    e = cudaMemset(st.status, 0, sizeof(words));
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  return static_cast<int>(words[0]);
+}
+
+const char* fa_b200_strerror(int code) {
+  switch (code) {
+    case FA_B200_OK: return "ok";
+    case FA_B200_ERR_NULL: return "fa_b200: params, q, k, v or o is NULL";
+    case FA_B200_ERR_HEAD_DIM: return "fa_b200: head dimension must be 64";
+    case FA_B200_ERR_SHAPE: return "fa_b200: B, H, N must be non-negative and within kernel limits";
+    case FA_B200_ERR_STRIDE: return "fa_b200: strides must be positive multiples of 8 elements (16 bytes)";
+    case FA_B200_ERR_ALIGN: return "fa_b200: q, k, v, o must be 16-byte aligned (lse 4-byte)";
+    case FA_B200_ERR_SCALE: return "fa_b200: softmax_scale must be finite and >= 0 (0 selects 1/sqrt(d))";
+    case FA_B200_ERR_DEVICE: return "fa_b200: bad device ordinal";
+    case FA_B200_ERR_ARCH: return "fa_b200: device is not compute capability 10.x (B200); there is no fallback";
+    case FA_B200_ERR_TENSORMAP: return "fa_b200: the driver rejected a TMA tensor map (check strides and sizes)";
+    case FA_B200_ERR_DRIVER: return "fa_b200: cuTensorMapEncodeTiled is not available from this driver";
+    default: break;
+  }
+  if (code > static_cast<int>(fa::kWatchdogBase)) {
+    switch (code & 0xff) {
+      case fa::kWaitQFull: return "fa_b200 watchdog: wait for the Q tile load ran out";
+      case fa::kWaitKVFull: return "fa_b200 watchdog: wait for a K/V tile load ran out";
+      case fa::kWaitKVEmpty: return "fa_b200 watchdog: wait for a free K/V slot ran out";
+      case fa::kWaitSFull: return "fa_b200 watchdog: wait for S = QK^T ran out";
+      case fa::kWaitPFull: return "fa_b200 watchdog: wait for P from the softmax warps ran out";
+      case fa::kWaitOFull: return "fa_b200 watchdog: wait for O += PV ran out";
+      default: return "fa_b200 watchdog: a bounded wait ran out";
+    }
+  }
+  if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+  return "fa_b200: unknown error code";
+}
+
+}  // extern "C"
