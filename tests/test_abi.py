@@ -1,0 +1,92 @@
+"""The C-ABI library: it loads, exports every symbol include/fa_b200.h declares, and rejects bad
+arguments before touching CUDA (so these run on a machine without a GPU)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from tfg_flashattention_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "fa_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fa_b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_all_exported(fa_lib):
+    declared = _declared_symbols()
+    assert set(_lib.EXPORTS) <= set(declared)
+    for name in declared:
+        assert hasattr(fa_lib, name), f"{name} declared in include/fa_b200.h but not exported"
+
+
+def test_abi_version(fa_lib):
+    assert fa_lib.fa_b200_abi_version() == _lib.ABI_VERSION
+
+
+def _good_params():
+    p = _lib.FaParams()
+    p.q, p.k, p.v, p.o = 0x1000, 0x2000, 0x3000, 0x4000
+    p.lse = None
+    p.B, p.H, p.N, p.d = 2, 3, 100, 64
+    for name in ("q_strides", "k_strides", "v_strides", "o_strides"):
+        setattr(p, name, (ctypes.c_int64 * 3)(3 * 100 * 64, 100 * 64, 64))
+    p.softmax_scale = 0.0
+    p.causal = 1
+    p.device = 0
+    p.stream = None
+    return p
+
+
+def test_validate_accepts_good_params(fa_lib):
+    assert fa_lib.fa_b200_validate(ctypes.byref(_good_params())) == 0
+
+
+@pytest.mark.parametrize("mutate,code", [
+    (lambda p: setattr(p, "q", None), -1),
+    (lambda p: setattr(p, "o", None), -1),
+    (lambda p: setattr(p, "d", 128), -2),
+    (lambda p: setattr(p, "d", 32), -2),
+    (lambda p: setattr(p, "N", -1), -3),
+    (lambda p: setattr(p, "B", -5), -3),
+    (lambda p: setattr(p, "q_strides", (ctypes.c_int64 * 3)(100, 64, 60)), -4),
+    (lambda p: setattr(p, "v_strides", (ctypes.c_int64 * 3)(0, 6400, 64)), -4),
+    (lambda p: setattr(p, "o_strides", (ctypes.c_int64 * 3)(19200, 6400, -64)), -4),
+    (lambda p: setattr(p, "k", 0x2004), -5),
+    (lambda p: setattr(p, "lse", 0x5002), -5),
+    (lambda p: setattr(p, "softmax_scale", float("nan")), -6),
+    (lambda p: setattr(p, "softmax_scale", float("inf")), -6),
+    (lambda p: setattr(p, "softmax_scale", -1.0), -6),
+    (lambda p: setattr(p, "device", -1), -7),
+])
+def test_validate_rejects(fa_lib, mutate, code):
+    p = _good_params()
+    mutate(p)
+    assert fa_lib.fa_b200_validate(ctypes.byref(p)) == code
+    # fa_b200_fwd applies the same checks first and makes no CUDA call when they fail
+    assert fa_lib.fa_b200_fwd(ctypes.byref(p)) == code
+    assert _lib.strerror(code).startswith("fa_b200")
+
+
+def test_null_params_pointer(fa_lib):
+    assert fa_lib.fa_b200_validate(None) == -1
+    assert fa_lib.fa_b200_fwd(None) == -1
+
+
+def test_strerror_covers_codes(fa_lib):
+    assert _lib.strerror(0) == "ok"
+    for code in range(-10, 0):
+        assert "unknown" not in _lib.strerror(code)
+    assert "watchdog" in _lib.strerror(0x10004)
+
+
+def test_python_shim_rejects_cpu_and_dtype():
+    import torch
+    from tfg_flashattention_b200 import custom_flash_attn
+    q = torch.zeros(1, 1, 8, 64, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        custom_flash_attn.forward(q, q, q)
