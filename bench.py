@@ -1,0 +1,372 @@
+#!/usr/bin/env python
+"""Benchmark of the attention-forward hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-sweep]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One "step" = one causal attention forward over one batch of the headline workload: the attention
+problem of one GPT-2 XL layer at prefill, B=32 sequences PER GPU, H=25, N=1024, d=64, bf16
+(weak scaling: every GPU gets its own batch; (batch, head) problems are independent, so there is no
+collective on the data path -- NCCL is only used for the timing barrier and the max over ranks).
+Inputs are synthetic (seeded N(0,1)); 420 MB per GPU, larger than the 126 MB L2.
+
+Rank 0 prints ONE JSON line.  `value` is aggregate causal-adjusted TFLOP/s (2*B*H*N^2*d per
+forward) with inputs resident in HBM; `e2e` is the same metric through the public
+`custom_flash_attn.forward` call with host buffers (pinned host -> device copies of q, k, v and the
+device -> host copy of O inside the timed region); `roofline` compares the kernel with the
+measured bf16 tensor peak; `cpu_baseline` times the CPU oracle (a port of the reference's
+standard-PyTorch attention) on a bounded sample on this box's host cores; `extra.sweep` holds the
+other attention configurations (sharded over ranks by (batch, head)).
+
+`--impl reference` times that CPU implementation instead, on all host threads, one bounded sample
+per step, and prints the same line with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from tfg_flashattention_b200 import workloads  # noqa: E402
+
+METRIC = "causal_attention_fwd_tflops"
+UNIT = "TFLOP/s"
+# DRAM bytes per launch of fa_fwd_kernel on the headline workload, from the ncu capture summarised
+# under profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); None until captured.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+CPU_SAMPLE_BATCH = 4          # batch entries (x25 heads) the CPU legs compute per repetition
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return {"bf16_tflops": float(p["bf16_tflops"]), "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", 0)),
+                "hbm_gbs": float(p["hbm_gbs"]), "source": "measured"}
+    except Exception:
+        return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: str):
+        self.index = index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0=None, t1=None):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        rows = [l for (t, l) in self.lines if (t0 is None or t >= t0 - 0.05) and (t1 is None or t <= t1 + 0.15)]
+        if not rows:
+            rows = [l for (_, l) in self.lines]
+        sm, smax, reasons, power = [], [], set(), []
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in rows:
+            f = [x.strip() for x in r.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[0])); smax.append(float(f[1])); power.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_setup(n_gpus):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    elif n_gpus > 1:
+        raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    return world, rank, local
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(x: float, world: int) -> float:
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def device_inputs(w, rank, heads=None):
+    """bf16 device tensors of workload w (seed offset by rank for per-GPU batches)."""
+    g = torch.Generator(device="cuda").manual_seed(w.seed + 1000 * rank)
+    shape = (w.B, w.H, w.N, w.d) if heads is None else (heads, 1, w.N, w.d)
+    q, k, v = (torch.randn(shape, device="cuda", generator=g, dtype=torch.float32).bfloat16() for _ in range(3))
+    if w.stress_k_rows:
+        idx = torch.randperm(w.N, device="cuda", generator=g)[: max(1, w.N // 100)]
+        k[:, :, idx, :] *= 4.0
+    return q, k, v
+
+
+def time_kernel(cfa, q, k, v, causal, steps, warmup, world):
+    """ms per step, max over ranks; CUDA events on the launching (current torch) stream."""
+    o = torch.empty_like(q)
+    for _ in range(warmup):
+        cfa.forward(q, k, v, causal=causal, out=o)
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        cfa.forward(q, k, v, causal=causal, out=o)
+    e1.record()
+    barrier(world)
+    ms = e0.elapsed_time(e1) / steps
+    return max_over_ranks(ms, world)
+
+
+def time_e2e(cfa, w, rank, steps, warmup, world):
+    """ms per step through the public call with HOST buffers: pinned q, k, v -> device, forward,
+    O -> pinned host, all inside the timed region."""
+    qd, kd, vd = device_inputs(w, rank)
+    hq, hk, hv = (t.cpu().pin_memory() for t in (qd, kd, vd))
+    ho = torch.empty_like(hq).pin_memory()
+    del qd, kd, vd
+
+    def step():
+        q = hq.to("cuda", non_blocking=True)
+        k = hk.to("cuda", non_blocking=True)
+        v = hv.to("cuda", non_blocking=True)
+        o = cfa.forward(q, k, v)
+        ho.copy_(o, non_blocking=True)
+
+    for _ in range(max(1, warmup)):
+        step()
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    barrier(world)
+    ms = max_over_ranks(e0.elapsed_time(e1) / steps, world)
+    nbytes = hq.numel() * 2
+    return ms, 3 * nbytes, nbytes
+
+
+def cpu_attention_sample(w, reps, threads):
+    """Time the CPU oracle on CPU_SAMPLE_BATCH batch entries of workload w.  Returns TFLOP/s."""
+    from oracle.attention_oracle import manual_attention
+    torch.set_num_threads(threads)
+    bs = min(CPU_SAMPLE_BATCH, w.B)
+    g = torch.Generator().manual_seed(w.seed)
+    q, k, v = (torch.randn(bs, w.H, w.N, w.d, generator=g) for _ in range(3))
+    flops = 2.0 * bs * w.H * w.N * w.N * w.d
+    manual_attention(q[:1], k[:1], v[:1], causal=True)           # warm the thread pool
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        manual_attention(q, k, v, causal=True)
+        times.append(time.perf_counter() - t0)
+    return flops / statistics.median(times) / 1e12, bs, times
+
+
+def run_reference(args, w):
+    """The reference arm: the reference's standard-PyTorch attention (CPU port in oracle/) on all
+    host threads; one bounded sample per step."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    from oracle.attention_oracle import manual_attention
+    torch.set_num_threads(threads)
+    bs = min(CPU_SAMPLE_BATCH, w.B)
+    g = torch.Generator().manual_seed(w.seed)
+    q, k, v = (torch.randn(bs, w.H, w.N, w.d, generator=g) for _ in range(3))
+    flops = 2.0 * bs * w.H * w.N * w.N * w.d
+    for _ in range(args.warmup):
+        manual_attention(q, k, v, causal=True)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        manual_attention(q, k, v, causal=True)
+    dt = (time.perf_counter() - t0) / args.steps
+    val = flops / dt / 1e12
+    sample = f"{bs} of {w.B} batch entries ({bs * w.H} of {w.B * w.H} heads) per step, fp32, torch CPU"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": w.name, "B_per_gpu": w.B, "H": w.H, "N": w.N, "d": w.d, "causal": True,
+                   "note": "CPU implementation; runs on rank 0 only, value does not scale with --gpus"},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-sweep", action="store_true", help="skip the extra configurations")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    w = workloads.config4_attention()
+    if args.impl == "reference":
+        run_reference(args, w)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the attention kernel has no CPU fallback")
+    world, rank, local = dist_setup(args.gpus)
+    torch.cuda.set_device(local)
+    from tfg_flashattention_b200 import custom_flash_attn as cfa
+    peaks = load_peaks()
+
+    # ---------------------------------------------------------------- headline: kernel, HBM-resident
+    q, k, v = device_inputs(w, rank)
+    try:
+        gpu_id = "GPU-" + str(torch.cuda.get_device_properties(torch.cuda.current_device()).uuid)
+    except Exception:
+        gpu_id = str(torch.cuda.current_device())
+    sampler = ClockSampler(gpu_id)
+    sampler.start()
+    time.sleep(0.3)
+    t0 = time.time()
+    ms = time_kernel(cfa, q, k, v, True, args.steps, args.warmup, world)
+    t1 = time.time()
+    clocks = sampler.stop(t0, t1)
+    status = cfa.last_status()
+    if status != 0:
+        raise SystemExit(f"kernel watchdog reported {status:#x}")
+    flops = w.flops()
+    value = world * flops / (ms * 1e-3) / 1e12
+    per_gpu = value / world
+    del q, k, v
+
+    # ---------------------------------------------------------------- end to end with host buffers
+    e2e_ms, h2d, d2h = time_e2e(cfa, w, rank, max(3, min(args.steps, 10)), 2, world)
+    e2e_value = world * flops / (e2e_ms * 1e-3) / 1e12
+
+    # ---------------------------------------------------------------- the other attention configs
+    sweep = []
+    if not args.no_sweep:
+        cases = [workloads.config1()]
+        cases += [workloads.config3(n, c) for n in (512, 1024, 2048, 4096) for c in (True, False)]
+        cases += [workloads.config5(n) for n in (8192, 16384, 32768)]
+        for cw in cases:
+            sl = workloads.shard_heads(cw.B * cw.H, world, rank)
+            heads = sl.stop - sl.start
+            steps = 20 if cw.N <= 4096 else (8 if cw.N <= 8192 else 4)
+            if heads > 0:
+                cq, ck, cv = device_inputs(cw, rank, heads=heads)
+                cms = time_kernel(cfa, cq, ck, cv, cw.causal, steps, 3, world)
+                del cq, ck, cv
+            else:
+                barrier(world); barrier(world)
+                cms = max_over_ranks(0.0, world)
+            tf = cw.flops() / (cms * 1e-3) / 1e12
+            sweep.append({"workload": cw.name, "B": cw.B, "H": cw.H, "N": cw.N, "causal": cw.causal,
+                          "ms": round(cms, 4), "tflops": round(tf, 1),
+                          "frac_of_peak_per_gpu": round(tf / world / peaks["bf16_tflops"], 4)})
+        if cfa.last_status() != 0:
+            raise SystemExit("kernel watchdog fired during the sweep")
+
+    # ---------------------------------------------------------------- CPU baseline (rank 0, N=1 only)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        threads = os.cpu_count() or 1
+        tf, bs, times = cpu_attention_sample(w, reps=5, threads=threads)
+        cpu = {"value": tf, "unit": UNIT, "cores": threads, "kind": "port",
+               "sample": f"{bs} of {w.B} batch entries ({bs * w.H} of {w.B * w.H} heads), "
+                         f"median of {len(times)} repetitions, fp32 torch CPU"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "gpt2-xl-layer-attention (config 4 attention shape)",
+                       "B_per_gpu": w.B, "H": w.H, "N": w.N, "d": w.d, "causal": True,
+                       "flops_convention": "causal-adjusted 2*B*H*N^2*d",
+                       "l2_policy": "inputs (420 MB per GPU) larger than L2 (126 MB)",
+                       "sharding": "independent (batch, head) problems per GPU, no collective"},
+            "tflops_per_gpu": per_gpu,
+            "frac_of_bf16_peak": per_gpu / peaks["bf16_tflops"],
+            "frac_of_bf16_peak_sustained": (per_gpu / peaks["bf16_tflops_sustained"]) if peaks["bf16_tflops_sustained"] else None,
+            "frac_of_bf16_nominal_2250": per_gpu / 2250.0,
+            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["bf16_tflops"],
+                         "unit": "TFLOP/s", "frac": per_gpu / peaks["bf16_tflops"],
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": f"of {peaks['source']}",
+                         "algorithmic_bytes": w.bytes(), "kernel": "fa::fa_fwd_kernel"},
+            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": args.steps,
+            "clocks": clocks,
+            "cpu_baseline": cpu,
+            "extra": {"sweep": sweep},
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
