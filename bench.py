@@ -264,6 +264,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-sweep", action="store_true", help="skip the extra configurations")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--case", default=None, metavar="B,H,N,causal",
+                    help="time only this attention problem (small runs for profilers); prints a short line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -278,6 +280,16 @@ def main():
     torch.cuda.set_device(local)
     from tfg_flashattention_b200 import custom_flash_attn as cfa
     peaks = load_peaks()
+
+    if args.case:
+        cb, ch, cn, cc = (int(x) for x in args.case.split(","))
+        cw = workloads.AttnWorkload("case", cb, ch, cn, seed=5, causal=bool(cc))
+        cq, ck, cv = device_inputs(cw, rank)
+        cms = time_kernel(cfa, cq, ck, cv, cw.causal, args.steps, args.warmup, world)
+        if rank == 0:
+            print(json.dumps({"case": args.case, "ms_per_step": cms, "tflops": cw.flops() / cms / 1e9,
+                              "status": cfa.last_status()}), flush=True)
+        return
 
     # ---------------------------------------------------------------- headline: kernel, HBM-resident
     q, k, v = device_inputs(w, rank)

@@ -69,6 +69,13 @@ void init_device(int dev) {
   cudaError_t e = cudaGetDeviceProperties(&prop, dev);
   if (e != cudaSuccess) { st.init_error = static_cast<int>(e); return; }
   if (prop.major != 10) { st.init_error = FA_B200_ERR_ARCH; return; }
+  // The kernel moves registers between its warpgroups with setmaxnreg; that only works (and
+  // otherwise blocks for ever) if the compiler gave the kernel the launch allocation the budget
+  // in fa_fwd_sm100.cuh assumes.  Refuse to launch a build where it did not.
+  cudaFuncAttributes fattr;
+  e = cudaFuncGetAttributes(&fattr, fa::fa_fwd_kernel);
+  if (e != cudaSuccess) { st.init_error = static_cast<int>(e); return; }
+  if (fattr.numRegs < fa::kLaunchRegs) { st.init_error = FA_B200_ERR_BUILD; return; }
   e = cudaFuncSetAttribute(fa::fa_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            fa::kSmemBytes);
   if (e != cudaSuccess) { st.init_error = static_cast<int>(e); return; }
@@ -201,6 +208,19 @@ int fa_b200_last_status(int device, void* stream) {
   return static_cast<int>(words[0]);
 }
 
+#ifdef FA_TRACE
+// Trace builds only: choose the traced CTA / copy the trace buffer to the host (synchronises).
+int fa_b200_trace_select(int block) {
+  return static_cast<int>(cudaMemcpyToSymbol(fa::g_fa_trace_block, &block, sizeof(int)));
+}
+int fa_b200_trace_read(unsigned long long* out, int n) {
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (n > fa::kTraceSlots) n = fa::kTraceSlots;
+  return static_cast<int>(cudaMemcpyFromSymbol(out, fa::g_fa_trace, sizeof(unsigned long long) * n));
+}
+#endif
+
 const char* fa_b200_strerror(int code) {
   switch (code) {
     case FA_B200_OK: return "ok";
@@ -214,6 +234,7 @@ const char* fa_b200_strerror(int code) {
     case FA_B200_ERR_ARCH: return "fa_b200: device is not compute capability 10.x (B200); there is no fallback";
     case FA_B200_ERR_TENSORMAP: return "fa_b200: the driver rejected a TMA tensor map (check strides and sizes)";
     case FA_B200_ERR_DRIVER: return "fa_b200: cuTensorMapEncodeTiled is not available from this driver";
+    case FA_B200_ERR_BUILD: return "fa_b200: the kernel was compiled with an unexpected register allocation; rebuild the library";
     default: break;
   }
   if (code > static_cast<int>(fa::kWatchdogBase)) {
