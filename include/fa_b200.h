@@ -49,7 +49,7 @@ extern "C" {
 #define FA_B200_ERR_ARCH          -8  /* device is not compute capability 10.x             */
 #define FA_B200_ERR_TENSORMAP     -9  /* the driver refused a TMA descriptor               */
 #define FA_B200_ERR_DRIVER       -10  /* cuTensorMapEncodeTiled could not be resolved      */
-#define FA_B200_ERR_BUILD        -11  /* library built with an unexpected register budget  */
+#define FA_B200_ERR_BUILD        -11  /* kernel image / launch configuration mismatch         */
 
 typedef struct fa_b200_params {
   const void* q;            /* bf16 [B,H,N,d] */

@@ -69,16 +69,17 @@ void init_device(int dev) {
   cudaError_t e = cudaGetDeviceProperties(&prop, dev);
   if (e != cudaSuccess) { st.init_error = static_cast<int>(e); return; }
   if (prop.major != 10) { st.init_error = FA_B200_ERR_ARCH; return; }
-  // The kernel moves registers between its warpgroups with setmaxnreg; that only works (and
-  // otherwise blocks for ever) if the compiler gave the kernel the launch allocation the budget
-  // in fa_fwd_sm100.cuh assumes.  Refuse to launch a build where it did not.
-  cudaFuncAttributes fattr;
-  e = cudaFuncGetAttributes(&fattr, fa::fa_fwd_kernel);
-  if (e != cudaSuccess) { st.init_error = static_cast<int>(e); return; }
-  if (fattr.numRegs < fa::kLaunchRegs) { st.init_error = FA_B200_ERR_BUILD; return; }
   e = cudaFuncSetAttribute(fa::fa_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            fa::kSmemBytes);
   if (e != cudaSuccess) { st.init_error = static_cast<int>(e); return; }
+  // Two CTAs per SM each allocate half of tensor memory; a third resident CTA would block in
+  // tcgen05.alloc until one of them exits.  Shared memory already limits residency to two; make
+  // sure of it (a build with a much smaller footprint would break that assumption).
+  int resident = 0;
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, fa::fa_fwd_kernel, fa::kNumThreads,
+                                                    fa::kSmemBytes);
+  if (e != cudaSuccess) { st.init_error = static_cast<int>(e); return; }
+  if (resident < 1 || resident > fa::kCtasPerSm) { st.init_error = FA_B200_ERR_BUILD; return; }
   void* addr = nullptr;
   e = cudaGetSymbolAddress(&addr, g_fa_status);
   if (e != cudaSuccess) { st.init_error = static_cast<int>(e); return; }
@@ -121,7 +122,7 @@ int fa_b200_validate(const fa_b200_params* p) {
   if (p->B < 0 || p->H < 0 || p->N < 0) return FA_B200_ERR_SHAPE;
   if (p->N > (1 << 24)) return FA_B200_ERR_SHAPE;
   {
-    const long long ctas = static_cast<long long>(p->B) * p->H * ((p->N + 255) / 256);
+    const long long ctas = static_cast<long long>(p->B) * p->H * ((p->N + 127) / 128);
     if (ctas > 0x7fffffffLL) return FA_B200_ERR_SHAPE;
   }
   if (!stride_ok(p->q_strides) || !stride_ok(p->k_strides) || !stride_ok(p->v_strides) ||
@@ -164,13 +165,13 @@ int fa_b200_fwd(const fa_b200_params* p) {
   kp.B = p->B;
   kp.H = p->H;
   kp.N = p->N;
-  kp.n_pairs = (p->N + 2 * fa::kBlockM - 1) / (2 * fa::kBlockM);
+  kp.n_qtiles = (p->N + fa::kBlockM - 1) / fa::kBlockM;
   kp.causal = p->causal ? 1 : 0;
   const float scale = p->softmax_scale > 0.0f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(p->d));
   kp.scale_log2 = scale * 1.4426950408889634f;
   kp.status = st.status;
 
-  const unsigned grid = static_cast<unsigned>(static_cast<long long>(p->B) * p->H * kp.n_pairs);
+  const unsigned grid = static_cast<unsigned>(static_cast<long long>(p->B) * p->H * kp.n_qtiles);
   fa::fa_fwd_kernel<<<grid, fa::kNumThreads, fa::kSmemBytes, static_cast<cudaStream_t>(p->stream)>>>(
       mq, mk, mv, kp);
   return static_cast<int>(cudaGetLastError());
@@ -234,7 +235,7 @@ const char* fa_b200_strerror(int code) {
     case FA_B200_ERR_ARCH: return "fa_b200: device is not compute capability 10.x (B200); there is no fallback";
     case FA_B200_ERR_TENSORMAP: return "fa_b200: the driver rejected a TMA tensor map (check strides and sizes)";
     case FA_B200_ERR_DRIVER: return "fa_b200: cuTensorMapEncodeTiled is not available from this driver";
-    case FA_B200_ERR_BUILD: return "fa_b200: the kernel was compiled with an unexpected register allocation; rebuild the library";
+    case FA_B200_ERR_BUILD: return "fa_b200: the kernel image does not match this library's launch configuration; rebuild it";
     default: break;
   }
   if (code > static_cast<int>(fa::kWatchdogBase)) {
