@@ -89,15 +89,31 @@ def test_parity_lengths(cfa, N, causal):
 
 
 def test_golden_vectors_from_reference(cfa, golden_dir):
-    """Inputs and outputs captured from the reference's own manual branch."""
+    """Inputs and outputs captured from the reference's own manual branch (fp32 on the CPU).
+
+    The kernel, like the reference's CUDA path under autocast, receives bf16 inputs.  These
+    fixtures have sharply peaked softmaxes (projection weights scaled x3) and |O| up to 6, so the
+    bf16 rounding of q and k alone moves O by up to ~2.5e-2.  Two checks therefore:
+      (i)  against the oracle -- bit-identical to the fixture on fp32 inputs, see test_oracle.py
+           -- evaluated on the same bf16-rounded inputs the kernel sees, at the reference tests'
+           tolerance rtol = atol = 1e-2 (test_cuda_implementation.py:90);
+      (ii) against the fixture's fp32 output itself: the kernel may add at most MAX_ABS to the
+           error that rounding the inputs to bf16 causes by itself (measured here with the
+           oracle)."""
     g = np.load(os.path.join(golden_dir, "attn_manual_cases.npz"))
+    orc = _oracle()
     for c in range(len(g["shapes"])):
         q, k, v, o_ref = (torch.from_numpy(g[f"{x}_{c}"]) for x in "qkvo")
-        o = cfa.forward(*(t.to("cuda", torch.bfloat16) for t in (q, k, v))).float().cpu()
+        qb, kb, vb = (t.to("cuda", torch.bfloat16) for t in (q, k, v))
+        o = cfa.forward(qb, kb, vb).float().cpu()
         assert cfa.last_status() == 0
-        # |O| reaches 6 here (bf16 half-ulp 1.6e-2 above 4): the reference tests' own tolerance
-        assert torch.allclose(o_ref, o, rtol=1e-2, atol=1e-2), \
-            f"case {c}: max diff {(o - o_ref).abs().max().item():.3e}"
+        o_rounded_inputs = orc.manual_attention(qb.float().cpu(), kb.float().cpu(), vb.float().cpu())
+        assert torch.allclose(o_rounded_inputs, o, rtol=1e-2, atol=1e-2), \
+            f"case {c}: max diff vs oracle on bf16 inputs {(o - o_rounded_inputs).abs().max().item():.3e}"
+        input_rounding = (o_rounded_inputs - o_ref).abs().max().item()
+        total = (o - o_ref).abs().max().item()
+        assert total <= input_rounding + MAX_ABS, \
+            f"case {c}: max diff vs reference fp32 output {total:.3e} (input rounding alone {input_rounding:.3e})"
 
 
 def test_config1_gpt2_small_shape(cfa):
@@ -155,11 +171,18 @@ def test_long_context_stress_rows(cfa):
     rows = torch.cat([torch.randint(0, w.N, (512,), generator=g), big, (big + 1).clamp_max(w.N - 1),
                       torch.tensor([0, 127, 128, 8191])]).unique()
     for h in range(2):
+        # The x4 key rows sharpen the softmax so much that rounding q and k to bf16 alone moves O
+        # by more than 2e-2 in places; the kernel is therefore held to the tolerance against the
+        # oracle on the bf16-rounded inputs it actually receives, and against the fp32-input
+        # oracle it may add at most that tolerance to the input-rounding error.
         ro, rl = orc.manual_attention_rows(q[0, h], k[0, h], v[0, h], rows)
-        d = (o[0, h, rows].float().cpu() - ro).abs()
-        assert d.max().item() <= MAX_ABS and d.mean().item() <= MEAN_ABS
         rb, rlb = orc.manual_attention_rows(qb[0, h].float().cpu(), kb[0, h].float().cpu(),
                                             vb[0, h].float().cpu(), rows)
+        got = o[0, h, rows].float().cpu()
+        d = (got - rb).abs()
+        assert d.max().item() <= MAX_ABS and d.mean().item() <= MEAN_ABS
+        assert (got - ro).abs().max().item() <= (rb - ro).abs().max().item() + MAX_ABS
+        assert (got - ro).abs().mean().item() <= (rb - ro).abs().mean().item() + MEAN_ABS
         assert ((lse[0, h, rows].cpu() - rlb).abs() <= 1e-3 * rlb.abs().clamp_min(1.0)).all()
 
 
