@@ -41,9 +41,10 @@ from tfg_flashattention_b200 import workloads  # noqa: E402
 
 METRIC = "causal_attention_fwd_tflops"
 UNIT = "TFLOP/s"
-# DRAM bytes per launch of fa_fwd_kernel on the headline workload, from the ncu capture summarised
-# under profiles/ (dram__bytes_read.sum + dram__bytes_write.sum); None until captured.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# DRAM bytes per launch of fa_fwd_kernel on the headline workload (dram__bytes_read.sum +
+# dram__bytes_write.sum).  Captured with ncu at B=12 (139.27 MB per launch) and scaled by 32/12 to
+# the benchmark's B=32: every (batch, head) is independent, so traffic grows in proportion.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 139.27e6 * 32 / 12
 CPU_SAMPLE_BATCH = 4          # batch entries (x25 heads) the CPU legs compute per repetition
 
 
