@@ -341,6 +341,38 @@ def main():
         if cfa.last_status() != 0:
             raise SystemExit("kernel watchdog fired during the sweep")
 
+    # ---------------------------------------------------------------- GPT-2 prefill (the callers)
+    prefill = []
+    if not args.no_sweep:
+        from tfg_flashattention_b200 import gpt2
+        for name, batch, seed, steps in (("gpt2-small", 8, 1, 5), ("gpt2-xl", 32, 3, 3)):
+            cfg = gpt2.gpt2_config(name, impl_type="cuda")
+            model = gpt2.init_random(gpt2.GPTModel(cfg, dtype=torch.bfloat16), seed=seed).cuda().eval()
+            ids = torch.randint(0, cfg["vocab_size"], (batch, 1024),
+                                generator=torch.Generator().manual_seed(seed + rank)).cuda()
+            with torch.no_grad():
+                for _ in range(2):
+                    model(ids)
+                barrier(world)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(steps):
+                    logits = model(ids)
+                e1.record()
+                barrier(world)
+            pms = max_over_ranks(e0.elapsed_time(e1) / steps, world)
+            tok_s = world * batch * 1024 / (pms * 1e-3)
+            prefill.append({"model": name, "batch_per_gpu": batch, "seq_len": 1024, "dtype": "bf16",
+                            "weights": f"random N(0,0.02) seed {seed}", "ms_per_forward": round(pms, 3),
+                            "tokens_per_s": round(tok_s, 1),
+                            "model_tflops_per_gpu": round(tok_s / world * gpt2.prefill_flops_per_token(cfg, 1024) / 1e12, 1),
+                            "attention": "fa::fa_fwd_kernel on strided [B,N,H,d] views, every layer",
+                            "logits": "all positions"})
+            del model, ids, logits
+            torch.cuda.empty_cache()
+        if cfa.last_status() != 0:
+            raise SystemExit("kernel watchdog fired during the prefill runs")
+
     # ---------------------------------------------------------------- CPU baseline (rank 0, N=1 only)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -373,7 +405,7 @@ def main():
             "gpu_launches": args.steps,
             "clocks": clocks,
             "cpu_baseline": cpu,
-            "extra": {"sweep": sweep},
+            "extra": {"sweep": sweep, "gpt2_prefill": prefill},
         }
         print(json.dumps(line), flush=True)
     if world > 1:

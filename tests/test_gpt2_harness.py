@@ -1,0 +1,79 @@
+"""The GPT-2 harness (the caller of the hot path) against the reference's own model output."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from tfg_flashattention_b200 import gpt2
+
+
+def _load_tiny(golden_dir, impl):
+    t = np.load(os.path.join(golden_dir, "gpt_tiny.npz"))
+    cfg = {"vocab_size": 97, "context_length": 48, "emb_dim": 128, "n_heads": int(t["n_heads"]),
+           "n_layers": int(t["n_layers"]), "drop_rate": 0.0, "qkv_bias": True, "impl_type": impl}
+    model = gpt2.GPTModel(cfg).eval()
+    sd = {k[3:]: torch.from_numpy(t[k]) for k in t.files if k.startswith("sd.")}
+    missing, unexpected = model.load_state_dict(sd, strict=True)
+    return model, torch.from_numpy(t["ids"]), torch.from_numpy(t["logits"])
+
+
+@pytest.mark.parametrize("impl", ["manual", "functional"])
+def test_harness_loads_reference_state_dict_and_matches_logits(golden_dir, impl):
+    """Same parameter names as the reference GPTModel; same logits on the CPU in fp32."""
+    model, ids, logits_ref = _load_tiny(golden_dir, impl)
+    with torch.no_grad():
+        logits = model(ids)
+    torch.testing.assert_close(logits, logits_ref, rtol=1e-4, atol=2e-5)
+
+
+def test_last_token_only(golden_dir):
+    model, ids, logits_ref = _load_tiny(golden_dir, "manual")
+    with torch.no_grad():
+        last = model(ids, last_token_only=True)
+    torch.testing.assert_close(last, logits_ref[:, -1:, :], rtol=1e-4, atol=2e-5)
+
+
+def test_configs_and_flops():
+    cfg = gpt2.gpt2_config("gpt2-xl")
+    assert (cfg["emb_dim"], cfg["n_layers"], cfg["n_heads"]) == (1600, 48, 25)
+    assert cfg["emb_dim"] // cfg["n_heads"] == 64
+    assert abs(gpt2.prefill_flops_per_token(cfg, 1024) - (3.11e9 + 1.57e8)) / 3.27e9 < 0.01
+    small = gpt2.gpt2_config("gpt2-small")
+    assert abs(gpt2.prefill_flops_per_token(small, 1024) - (2.47e8 + 1.89e7)) / 2.66e8 < 0.01
+
+
+@pytest.mark.gpu
+def test_harness_with_cuda_kernel_matches_reference_logits(golden_dir, fa_lib):
+    """impl_type="cuda": every layer's attention runs through the sm_100a kernel (bf16 under
+    autocast, as in the reference); logits against the reference's fp32 CPU logits."""
+    model, ids, logits_ref = _load_tiny(golden_dir, "cuda")
+    model = model.cuda()
+    with torch.no_grad():
+        logits = model(ids.cuda()).float().cpu()
+    from tfg_flashattention_b200 import custom_flash_attn
+    assert custom_flash_attn.last_status() == 0
+    # bf16 attention + bf16 projections under autocast against fp32: logits are O(1)
+    assert (logits - logits_ref).abs().max().item() < 5e-2
+    assert (logits - logits_ref).abs().mean().item() < 5e-3
+    # and against the same model with torch's attention under the same autocast recipe
+    model_f, _, _ = _load_tiny(golden_dir, "functional")
+    with torch.no_grad():
+        logits_f = model_f.cuda()(ids.cuda()).float().cpu()
+    assert (logits - logits_f).abs().max().item() < 3e-2
+
+
+@pytest.mark.gpu
+def test_bf16_model_prefill_small(fa_lib):
+    """GPT-2 small, random init, whole model in bf16: "cuda" against "functional"."""
+    cfg = gpt2.gpt2_config("gpt2-small")
+    cfg["n_layers"] = 2
+    m = gpt2.init_random(gpt2.GPTModel(cfg, dtype=torch.bfloat16), seed=1).cuda().eval()
+    ids = torch.randint(0, cfg["vocab_size"], (2, 1024), generator=torch.Generator().manual_seed(1)).cuda()
+    with torch.no_grad():
+        a = m(ids).float()
+        for blk in m.trf_blocks:
+            blk.att.impl_type = "functional"
+        b = m(ids).float()
+    assert torch.isfinite(a).all()
+    assert (a - b).abs().max().item() < 5e-2

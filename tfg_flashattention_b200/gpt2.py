@@ -1,0 +1,186 @@
+"""GPT-2 prefill harness: the caller of the attention hot path.
+
+Mirrors the reference's model (src/py/model_inference.py:39-190) module for module and parameter
+name for parameter name, so a reference state_dict loads unchanged:
+
+    MultiHeadAttention  :39-94    W_query / W_key / W_value / out_proj, impl_type dispatch
+    LayerNorm           :96-107   scale / shift, eps 1e-5, biased variance
+    GELU                :109-117  tanh form
+    FeedForward         :119-128  layers.0 / layers.2
+    TransformerBlock    :149-164  pre-LN, attention under bf16 autocast
+    GPTModel            :180-190  tok_emb + pos_emb -> trf_blocks -> final_norm -> out_head
+
+What differs, on purpose:
+  * impl_type "cuda" calls this package's `custom_flash_attn.forward` on the strided
+    `[B,N,H,d] -> transpose(1,2)` views directly.  The reference makes three `.contiguous()`
+    copies first (:86-90); the kernel reads the views in place through its TMA descriptors and
+    writes O in `[B,N,H,d]` memory, so the copy back is free as well.
+  * the reference's "cuda" and "triton" branches forget the `transpose(1, 2)` that its "manual"
+    and "functional" branches apply before `.view(b, n, d_out)` (:75, :80 against :83, :86-92),
+    which scrambles heads and tokens.  Parity is defined against the "manual" branch, so the
+    transpose is applied here.
+  * LayerNorm and GELU call the fused torch ops (same arithmetic, one kernel each).
+  * `GPTModel(cfg, dtype=torch.bfloat16)` builds the whole model in bf16 (the prefill benchmark
+    configuration); the default keeps the reference's precision recipe: fp32 everywhere, bf16
+    autocast around attention only (:153-154).
+
+"manual" and "functional" branches are kept for comparison on any device; "cuda" has no fallback.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+GPT2_SIZES = {   # model_inference.py:392-397
+    "gpt2-small": {"emb_dim": 768, "n_layers": 12, "n_heads": 12},
+    "gpt2-medium": {"emb_dim": 1024, "n_layers": 24, "n_heads": 16},
+    "gpt2-large": {"emb_dim": 1280, "n_layers": 36, "n_heads": 20},
+    "gpt2-xl": {"emb_dim": 1600, "n_layers": 48, "n_heads": 25},
+}
+
+
+def gpt2_config(name: str, impl_type: str = "cuda", context_length: int = 1024) -> dict:
+    """GPT_CONFIG_124M (:378-386) updated the way the reference driver does (:420-422)."""
+    cfg = {"vocab_size": 50257, "context_length": context_length, "drop_rate": 0.0,
+           "qkv_bias": True, "impl_type": impl_type}
+    cfg.update(GPT2_SIZES[name])
+    return cfg
+
+
+class MultiHeadAttention(nn.Module):
+    def __init__(self, d_in, d_out, context_length, dropout, num_heads, impl_type, qkv_bias=False):
+        super().__init__()
+        assert d_out % num_heads == 0, "d_out must be a multiple of num_heads"
+        self.head_dim = d_out // num_heads
+        self.num_heads = num_heads
+        self.d_out = d_out
+        self.impl_type = impl_type
+        self.W_query = nn.Linear(d_in, d_out, bias=qkv_bias)
+        self.W_key = nn.Linear(d_in, d_out, bias=qkv_bias)
+        self.W_value = nn.Linear(d_in, d_out, bias=qkv_bias)
+        self.out_proj = nn.Linear(d_out, d_out)
+        self.dropout = nn.Dropout(dropout)
+        self.context_length = context_length
+
+    def forward(self, x):
+        b, n, _ = x.shape
+        h, d = self.num_heads, self.head_dim
+        q = self.W_query(x).view(b, n, h, d).transpose(1, 2)
+        k = self.W_key(x).view(b, n, h, d).transpose(1, 2)
+        v = self.W_value(x).view(b, n, h, d).transpose(1, 2)
+        if self.impl_type == "cuda":
+            from . import custom_flash_attn
+            if q.dtype != torch.bfloat16:      # outside autocast: the kernel is bf16-only
+                q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
+            ctx = custom_flash_attn.forward(q, k, v).transpose(1, 2)     # [B,N,H,d], dense
+        elif self.impl_type == "manual":
+            attn = q @ k.transpose(-2, -1)
+            mask = torch.triu(torch.ones(n, n, device=x.device), diagonal=1).bool()
+            attn.masked_fill_(mask, -torch.inf)
+            w = self.dropout(torch.softmax(attn / k.shape[-1] ** 0.5, dim=-1))
+            ctx = (w @ v).transpose(1, 2)
+        elif self.impl_type == "functional":
+            ctx = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2)
+        else:
+            raise ValueError(f"unknown impl_type {self.impl_type!r}")
+        ctx = ctx.reshape(b, n, self.d_out)
+        if not torch.is_autocast_enabled():
+            ctx = ctx.to(self.out_proj.weight.dtype)
+        return self.out_proj(ctx)
+
+
+class LayerNorm(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.eps = 1e-5
+        self.scale = nn.Parameter(torch.ones(config["emb_dim"]))
+        self.shift = nn.Parameter(torch.zeros(config["emb_dim"]))
+
+    def forward(self, x):
+        return F.layer_norm(x, x.shape[-1:], self.scale, self.shift, self.eps)
+
+
+class GELU(nn.Module):
+    def forward(self, x):
+        return F.gelu(x, approximate="tanh")
+
+
+class FeedForward(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.layers = nn.Sequential(nn.Linear(config["emb_dim"], 4 * config["emb_dim"]), GELU(),
+                                    nn.Linear(4 * config["emb_dim"], config["emb_dim"]))
+
+    def forward(self, x):
+        return self.layers(x)
+
+
+class TransformerBlock(nn.Module):
+    def __init__(self, cfg, autocast_attention=True):
+        super().__init__()
+        self.att = MultiHeadAttention(cfg["emb_dim"], cfg["emb_dim"], cfg["context_length"],
+                                      cfg["drop_rate"], cfg["n_heads"], cfg["impl_type"], cfg["qkv_bias"])
+        self.ff = FeedForward(cfg)
+        self.norm1 = LayerNorm(cfg)
+        self.norm2 = LayerNorm(cfg)
+        self.drop_shortcut = nn.Dropout(cfg["drop_rate"])
+        self.autocast_attention = autocast_attention
+
+    def forward(self, x):
+        shortcut = x
+        h = self.norm1(x)
+        if self.autocast_attention and x.is_cuda and x.dtype == torch.float32:
+            with torch.autocast(device_type="cuda", dtype=torch.bfloat16):   # as the reference, :153
+                h = self.att(h)
+            h = h.to(x.dtype)
+        else:
+            h = self.att(h)
+        x = self.drop_shortcut(h) + shortcut
+        shortcut = x
+        x = self.drop_shortcut(self.ff(self.norm2(x))) + shortcut
+        return x
+
+
+class GPTModel(nn.Module):
+    def __init__(self, cfg, dtype=None):
+        super().__init__()
+        self.cfg = dict(cfg)
+        self.tok_emb = nn.Embedding(cfg["vocab_size"], cfg["emb_dim"])
+        self.pos_emb = nn.Embedding(cfg["context_length"], cfg["emb_dim"])
+        self.drop_emb = nn.Dropout(cfg["drop_rate"])
+        self.trf_blocks = nn.Sequential(*[TransformerBlock(cfg) for _ in range(cfg["n_layers"])])
+        self.final_norm = LayerNorm(cfg)
+        self.out_head = nn.Linear(cfg["emb_dim"], cfg["vocab_size"], bias=False)
+        if dtype is not None:
+            self.to(dtype)
+
+    def forward(self, in_idx, last_token_only=False):
+        _, n = in_idx.shape
+        x = self.tok_emb(in_idx) + self.pos_emb(torch.arange(n, device=in_idx.device))
+        x = self.trf_blocks(self.drop_emb(x))
+        x = self.final_norm(x)
+        if last_token_only:           # what generate() consumes (model_inference.py:206)
+            x = x[:, -1:, :]
+        return self.out_head(x)
+
+
+def init_random(model: GPTModel, seed: int, std: float = 0.02) -> GPTModel:
+    """Random-init weights N(0, std) from `seed` (LayerNorm scale 1 / shift 0, as the reference
+    initialises them, :100-101); stands in for the OpenAI checkpoints, which need the network."""
+    g = torch.Generator().manual_seed(seed)
+    with torch.no_grad():
+        for name, prm in model.named_parameters():
+            if name.endswith(".scale"):
+                prm.fill_(1.0)
+            elif name.endswith(".shift"):
+                prm.zero_()
+            else:
+                prm.copy_((torch.randn(prm.shape, generator=g) * std).to(prm.dtype))
+    return model
+
+
+def prefill_flops_per_token(cfg: dict, n: int) -> float:
+    """2*(12*L*d_model^2 + d_model*vocab) for the GEMMs + causal-adjusted attention 2*N*d_model*L."""
+    L, dm, vocab = cfg["n_layers"], cfg["emb_dim"], cfg["vocab_size"]
+    return 2.0 * (12.0 * L * dm * dm + dm * vocab) + 2.0 * n * dm * L
