@@ -7,6 +7,7 @@
 #include <cmath>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "../../include/fa_b200.h"
@@ -25,6 +26,7 @@ struct DeviceState {
   std::once_flag once;
   int init_error = 0;       // value fa_b200_fwd returns if set-up failed
   unsigned int* status = nullptr;  // device address of the watchdog words
+  int resident_ctas = 0;           // persistent grid size: CTAs per SM x SM count
 };
 
 DeviceState g_dev[kMaxDevices];
@@ -69,17 +71,34 @@ void init_device(int dev) {
   cudaError_t e = cudaGetDeviceProperties(&prop, dev);
   if (e != cudaSuccess) { st.init_error = static_cast<int>(e); return; }
   if (prop.major != 10) { st.init_error = FA_B200_ERR_ARCH; return; }
-  e = cudaFuncSetAttribute(fa::fa_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           fa::kSmemBytes);
-  if (e != cudaSuccess) { st.init_error = static_cast<int>(e); return; }
-  // Two CTAs per SM each allocate half of tensor memory; a third resident CTA would block in
-  // tcgen05.alloc until one of them exits.  Shared memory already limits residency to two; make
-  // sure of it (a build with a much smaller footprint would break that assumption).
-  int resident = 0;
-  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, fa::fa_fwd_kernel, fa::kNumThreads,
-                                                    fa::kSmemBytes);
-  if (e != cudaSuccess) { st.init_error = static_cast<int>(e); return; }
-  if (resident < 1 || resident > fa::kCtasPerSm) { st.init_error = FA_B200_ERR_BUILD; return; }
+  // The kernel moves registers between its warpgroups with setmaxnreg; that only works (and
+  // otherwise blocks for ever) if the compiler gave the kernel the launch allocation the budget
+  // in fa_fwd_sm100.cuh assumes.  Refuse to launch a build where it did not.
+  for (int variant = 0; variant < 2; ++variant) {
+    const void* fn = variant == 0 ? reinterpret_cast<const void*>(&fa::fa_fwd_kernel<false>)
+                                  : reinterpret_cast<const void*>(&fa::fa_fwd_kernel<true>);
+    cudaFuncAttributes fattr;
+    e = cudaFuncGetAttributes(&fattr, fn);
+    if (e != cudaSuccess) { st.init_error = static_cast<int>(e); return; }
+    if (fattr.numRegs != fa::kLaunchRegs) { st.init_error = FA_B200_ERR_BUILD; return; }
+    e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, fa::kSmemBytes);
+    if (e != cudaSuccess) { st.init_error = static_cast<int>(e); return; }
+    // Two CTAs of ~100 KB each must fit: ask for the largest shared-memory carveout.
+    e = cudaFuncSetAttribute(fn, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) { st.init_error = static_cast<int>(e); return; }
+    // Two CTAs per SM each allocate half of tensor memory; a third resident CTA would block in
+    // tcgen05.alloc until one of them exits.  Shared memory already limits residency to two; make
+    // sure of it (a build with a much smaller footprint would break that assumption).
+    int resident = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, fn, fa::kNumThreads, fa::kSmemBytes);
+    if (e != cudaSuccess) { st.init_error = static_cast<int>(e); return; }
+    if (resident < 1 || resident > fa::kCtasPerSm) { st.init_error = FA_B200_ERR_BUILD; return; }
+  }
+  // The persistent grid is sized for kCtasPerSm per SM whatever the occupancy query answered: it
+  // has been seen to answer 1 where the hardware co-schedules 2, and a CTA that has to wait for
+  // a slot only starts later -- work items are partitioned by grid stride, no CTA waits on another.
+  st.resident_ctas = fa::kCtasPerSm * prop.multiProcessorCount;
   void* addr = nullptr;
   e = cudaGetSymbolAddress(&addr, g_fa_status);
   if (e != cudaSuccess) { st.init_error = static_cast<int>(e); return; }
@@ -151,17 +170,14 @@ int fa_b200_fwd(const fa_b200_params* p) {
   std::call_once(g_encode_once, resolve_encode);
   if (g_encode == nullptr) return FA_B200_ERR_DRIVER;
 
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mo;
   if ((rc = encode_map(&mq, p->q, p, p->q_strides)) != 0) return rc;
   if ((rc = encode_map(&mk, p->k, p, p->k_strides)) != 0) return rc;
   if ((rc = encode_map(&mv, p->v, p, p->v_strides)) != 0) return rc;
+  if ((rc = encode_map(&mo, p->o, p, p->o_strides)) != 0) return rc;
 
   fa::FwdParams kp;
-  kp.o = static_cast<__nv_bfloat16*>(p->o);
   kp.lse = p->lse;
-  kp.o_sb = p->o_strides[0];
-  kp.o_sh = p->o_strides[1];
-  kp.o_sn = p->o_strides[2];
   kp.B = p->B;
   kp.H = p->H;
   kp.N = p->N;
@@ -171,9 +187,27 @@ int fa_b200_fwd(const fa_b200_params* p) {
   kp.scale_log2 = scale * 1.4426950408889634f;
   kp.status = st.status;
 
-  const unsigned grid = static_cast<unsigned>(static_cast<long long>(p->B) * p->H * kp.n_qtiles);
-  fa::fa_fwd_kernel<<<grid, fa::kNumThreads, fa::kSmemBytes, static_cast<cudaStream_t>(p->stream)>>>(
-      mq, mk, mv, kp);
+  const long long items = static_cast<long long>(p->B) * p->H * kp.n_qtiles;
+  kp.n_items = static_cast<int>(items);
+  // Persistent grid (2 CTAs per SM, each striding through the item list) when the items are
+  // many and short; otherwise one CTA per item, which the hardware balances dynamically.
+  // FA_B200_PERSISTENT=0/1 in the environment overrides the choice (for measurements).
+  static const int persistent_env = [] {
+    const char* e = std::getenv("FA_B200_PERSISTENT");
+    return e == nullptr ? -1 : (e[0] == '0' ? 0 : 1);
+  }();
+  const int kv_tiles = (p->N + fa::kBlockN - 1) / fa::kBlockN;
+  const bool auto_persistent = items >= 8LL * st.resident_ctas && kv_tiles <= 8;
+  const bool persistent = persistent_env < 0 ? auto_persistent : persistent_env == 1;
+  kp.rotate = (persistent && kp.causal) ? 1 : 0;
+  const cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+  if (persistent) {
+    const unsigned grid = static_cast<unsigned>(items < st.resident_ctas ? items : st.resident_ctas);
+    fa::fa_fwd_kernel<true><<<grid, fa::kNumThreads, fa::kSmemBytes, stream>>>(mq, mk, mv, mo, kp);
+  } else {
+    fa::fa_fwd_kernel<false><<<static_cast<unsigned>(items), fa::kNumThreads, fa::kSmemBytes, stream>>>(
+        mq, mk, mv, mo, kp);
+  }
   return static_cast<int>(cudaGetLastError());
 }
 

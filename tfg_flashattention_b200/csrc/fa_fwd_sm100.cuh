@@ -1,27 +1,34 @@
 // FlashAttention forward for sm_100a (B200), head dim 64, bf16 in / fp32 accumulate / bf16 out.
 //
-// One CTA owns one 128-row query tile of one (batch, head) and streams that head's K/V tiles
-// through shared memory.  Two CTAs are resident per SM (each takes 256 of the 512 TMEM columns,
-// under half the shared memory and half the registers), so one CTA's start-up, epilogue and
-// latency-bound phases run under the other CTA's tensor-core and MUFU work.
+// A work item is one 128-row query tile of one (batch, head); the CTA streams that head's K/V
+// tiles through shared memory.  Two CTAs are resident per SM (each takes 256 of the 512 TMEM
+// columns, under half the shared memory and half the registers), so one CTA's latency-bound
+// phases run under the other CTA's tensor-core and MUFU work.  The grid is either one CTA per
+// item or persistent (2 x SM count CTAs striding through a load-balanced item list); in the
+// persistent case every role runs ahead across item boundaries: the producer loads the next
+// item's Q/K/V, the issuer starts its first S, and the softmax warps run an item's epilogue in
+// the middle of the next item's first tile, when the last O += P V has long completed.
 //
-//   warp 5              TMA producer: the Q tile once, then K_j, V_j into a ring of 16 KB slots,
-//                       128-byte swizzle, completion on mbarriers (no multicast).
-//   warp 4              tcgen05 issuer: S = Q K_j^T (M128 N128 K64, both operands in shared
-//                       memory) and O += P V_j (M128 N64 K128, P read from tensor memory, V
-//                       MN-major from shared memory).  Control flow is warp-uniform; one elected
-//                       lane issues, tcgen05.commit signals the mbarriers.
-//   warps 0-3           softmax: one thread per query row.  Pulls its S row from TMEM into
-//                       registers and releases S at once, so the issuer can start S for the next
-//                       K tile while this one is exponentiated; keeps the running max and sum;
-//                       writes P (bf16) to its own TMEM columns; rescales O in TMEM only when the
-//                       running max grew by more than 2^8; finally writes O / l and the LSE.
+//   warpgroup 1, warp 5   TMA producer: Q, then K_j, V_j into a ring of 16 KB slots, 128-byte
+//                         swizzle, completion on mbarriers (no multicast).
+//   warpgroup 1, warp 4   tcgen05 issuer: S = Q K_j^T (M128 N128 K64, both operands in shared
+//                         memory) and O += P V_j (M128 N64 K128, P read from tensor memory, V
+//                         MN-major from shared memory).  Control flow is warp-uniform; one
+//                         elected lane issues, tcgen05.commit signals the mbarriers.
+//                         (warps 6, 7 idle: setmaxnreg works on whole warpgroups.)
+//   warpgroup 0           softmax, one thread per query row.  Pulls its S row from TMEM into
+//                         registers and releases S at once, so the issuer can start S for the
+//                         next K tile while this one is exponentiated; keeps the running max and
+//                         sum; writes P (bf16) to its own TMEM columns; rescales O in TMEM only
+//                         when the running max grew by more than 2^8; epilogue: O / l -> bf16 ->
+//                         swizzled shared-memory tile -> TMA store, and the LSE.
 //
 // TMEM columns (32-bit, 128 lanes):  S [0,128)  P [128,192)  O [192,256)
 //
 // Every mbarrier wait is bounded: a wait that exceeds kWaitLimitNs records a code in the status
 // word, raises the CTA's abort flag, and every role drains and leaves through the normal exit
-// (TMEM is freed).  Nothing traps and nothing spins without a limit.
+// (TMEM is freed).  Nothing traps and nothing spins without a limit.  The one hardware wait
+// without a limit, setmaxnreg.inc, is made safe by the static register budget below.
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -36,12 +43,22 @@ constexpr int kBlockM = 128;           // query rows per tile
 constexpr int kBlockN = 128;           // key/value rows per tile
 constexpr int kHeadDim = 64;           // fixed, as in the reference (common_types.hpp:33)
 constexpr int kTileBytes = kBlockN * kHeadDim * 2;
-constexpr int kKVSlots = 5;            // ring: K0 V0 K1 V1 ...
+constexpr int kKVSlots = 4;            // ring: K0 V0 K1 V1 ..., continuing across work items
 constexpr int kNumSoftmaxWarps = 4;
 constexpr int kMmaWarp = 4;
 constexpr int kLoadWarp = 5;
-constexpr int kNumThreads = 192;
+constexpr int kNumThreads = 256;       // two whole warpgroups
 constexpr int kCtasPerSm = 2;
+// Register budget.  Two 256-thread CTAs per SM start with 128 registers per thread; the softmax
+// warpgroup then takes kSoftmaxRegs and the other warpgroup keeps kOtherRegs.  setmaxnreg.inc can
+// only take registers that this CTA's own setmaxnreg.dec released and blocks -- with no time limit
+// -- until they exist, so the budget after the exchange must fit in the launch allocation.
+constexpr int kLaunchRegs = 128;
+constexpr int kSoftmaxRegs = 208;
+constexpr int kOtherRegs = 48;
+static_assert(128 * kSoftmaxRegs + 128 * kOtherRegs <= kNumThreads * kLaunchRegs,
+              "setmaxnreg budget exceeds the launch allocation: the kernel would hang");
+static_assert(kSoftmaxRegs % 8 == 0 && kOtherRegs % 8 == 0 && kOtherRegs >= 24, "setmaxnreg operands");
 constexpr uint32_t kTmemCols = 256;    // two resident CTAs share the SM's 512 columns
 constexpr uint32_t kTmemS = 0, kTmemP = 128, kTmemO = 192;
 constexpr float kRescaleThresholdLog2 = 8.0f;
@@ -51,19 +68,25 @@ constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
 constexpr uint32_t kWatchdogBase = 0x10000u;
 enum WaitId : uint32_t {
   kWaitQFull = 1, kWaitKVFull = 2, kWaitKVEmpty = 3, kWaitSFull = 4, kWaitPFull = 5,
-  kWaitOFull = 6, kWaitDrain = 7, kWaitSFree = 8
+  kWaitOFull = 6, kWaitDrain = 7, kWaitSFree = 8, kWaitQEmpty = 9, kWaitOFree = 10,
+  kWaitOStaged = 11, kWaitStageFree = 12
 };
 
 struct __align__(1024) SharedStorage {
   uint8_t q[kTileBytes];
   uint8_t kv[kKVSlots][kTileBytes];
+  uint8_t o_stage[kTileBytes];   // bf16 O tile, 128B-swizzled, source of the TMA store
   uint64_t q_full;
+  uint64_t q_empty;              // every S of the item that used the Q slot has completed
   uint64_t kv_full[kKVSlots];
   uint64_t kv_empty[kKVSlots];
   uint64_t s_full;               // S written by the tensor core
   uint64_t s_free;               // S copied to registers by all four softmax warps
   uint64_t p_full;               // P written to TMEM by all four softmax warps
   uint64_t o_full;               // O += P V_j finished (P reusable, O stable)
+  uint64_t o_free;               // the epilogue has read O: the next item may overwrite it
+  uint64_t o_staged;             // all four softmax warps have written their rows to o_stage
+  uint64_t stage_free;           // the previous TMA store has finished reading o_stage
   uint32_t tmem_base;
   uint32_t abort;
 };
@@ -71,11 +94,11 @@ constexpr int kSmemBytes = sizeof(SharedStorage) + 1024;  // + slack to align th
 static_assert(kCtasPerSm * (kSmemBytes + 1024) <= 227 * 1024, "two CTAs must fit in one SM");
 
 struct FwdParams {
-  __nv_bfloat16* o;
   float* lse;                 // may be null
-  long long o_sb, o_sh, o_sn; // element strides of O: batch, head, row
   int B, H, N;
-  int n_qtiles;               // ceil(N / 128): CTAs per (batch, head)
+  int n_qtiles;               // ceil(N / 128): work items per (batch, head)
+  int n_items;                // B * H * n_qtiles
+  int rotate;                 // causal + persistent grid: rotate the tile order per head
   int causal;
   float scale_log2;           // softmax_scale * log2(e)
   unsigned int* status;       // [4] watchdog words in global memory
@@ -136,9 +159,15 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// kPersistent = true: the grid is 2 x SM count and every role loops over work items (best when
+// items are many and short, e.g. N = 1024 causal: 4.5 K/V tiles per item on average).
+// kPersistent = false: one CTA per item, no cross-item state in the hot loop (best for long
+// sequences and for grids too small to balance statically).
+template <bool kPersistent>
 __global__ void __launch_bounds__(kNumThreads, kCtasPerSm)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-              const __grid_constant__ CUtensorMap tmap_v, const FwdParams p) {
+              const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
+              const FwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   SharedStorage& sm =
@@ -146,24 +175,38 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-
-  // ---- which rows does this CTA own?  Heaviest (latest) causal row tiles are launched first.
-  const int tile_slot = blockIdx.x % p.n_qtiles;
-  const int bh = blockIdx.x / p.n_qtiles;
-  const int qt = p.causal ? (p.n_qtiles - 1 - tile_slot) : tile_slot;
-  const int b = bh / p.H;
-  const int h = bh % p.H;
   const int nkv = (p.N + kBlockN - 1) / kBlockN;
-  const int q_row = qt * kBlockM;
-  const int ns = p.causal ? min(nkv, qt + 1) : nkv;   // K/V tiles this query tile attends to
+
+  // Work item -> (batch, head, query tile).  A head's tiles are adjacent in the list, so CTAs
+  // that run side by side share that head's K/V in L2.  In causal mode tile t costs t+1 K/V tiles
+  // and the heaviest tile of a head comes first; with a persistent grid the order inside a head
+  // is instead rotated by the head index, so that a CTA striding through the list by gridDim.x
+  // meets every cost equally often.
+  struct Item { int b, h, q_row, ns; };
+  auto decode = [&](int item) {
+    const int bh = item / p.n_qtiles;
+    const int slot = item - bh * p.n_qtiles;
+    int qt = slot;
+    if (p.causal) qt = p.n_qtiles - 1 - (p.rotate ? (slot + bh) % p.n_qtiles : slot);
+    Item w;
+    w.b = bh / p.H;
+    w.h = bh - w.b * p.H;
+    w.q_row = qt * kBlockM;
+    w.ns = p.causal ? min(nkv, qt + 1) : nkv;   // K/V tiles this query tile attends to
+    return w;
+  };
 
   // ---- one-time setup
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&sm.q_full), 1);
+    mbar_init(smem_u32(&sm.q_empty), 1);
     mbar_init(smem_u32(&sm.s_full), 1);
     mbar_init(smem_u32(&sm.s_free), kNumSoftmaxWarps);
     mbar_init(smem_u32(&sm.p_full), kNumSoftmaxWarps);
     mbar_init(smem_u32(&sm.o_full), 1);
+    mbar_init(smem_u32(&sm.o_free), kNumSoftmaxWarps);
+    mbar_init(smem_u32(&sm.o_staged), kNumSoftmaxWarps);
+    mbar_init(smem_u32(&sm.stage_free), 1);
     for (int i = 0; i < kKVSlots; ++i) {
       mbar_init(smem_u32(&sm.kv_full[i]), 1);
       mbar_init(smem_u32(&sm.kv_empty[i]), 1);
@@ -184,113 +227,145 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
   auto slot_of = [](int it) { return it % kKVSlots; };
   auto par_of = [](int it) { return static_cast<uint32_t>((it / kKVSlots) & 1); };
 
-  if (warp == kLoadWarp) {
-    // =================================================================== TMA producer
-    // ring order: K_0 V_0 K_1 V_1 ...  (K_j is load 2j, V_j is load 2j+1)
-    if (elect_one()) {
-      tma_prefetch_desc(&tmap_q);
-      tma_prefetch_desc(&tmap_k);
-      tma_prefetch_desc(&tmap_v);
-    }
-    bool ok = true;
-    int it = 0;
-    auto load_kv = [&](const CUtensorMap* map, int j) {
-      const int slot = slot_of(it);
-      const int use = it / kKVSlots;
-      if (use > 0 && ok)
-        ok = wait_bar_warp(smem_u32(&sm.kv_empty[slot]), (use - 1) & 1, watch, kWaitKVEmpty);
-      if (ok) {
-        if (elect_one()) {
-          const uint32_t bar = smem_u32(&sm.kv_full[slot]);
-          mbar_arrive_expect_tx(bar, kTileBytes);
-          tma_load_4d(smem_u32(sm.kv[slot]), map, bar, 0, j * kBlockN, h, b);
+  if (warp >= kNumSoftmaxWarps) {
+    reg_dealloc<kOtherRegs>();      // executed by all four warps of warpgroup 1
+    if (warp == kLoadWarp) {
+      // ================================================================= TMA producer
+      // K/V ring order: K_0 V_0 K_1 V_1 ... continuing across work items; `it` counts loads.
+      // One Q slot is enough to load the next item's Q early: it is free as soon as the current
+      // item's LAST S has completed, a whole softmax + PV + epilogue before the item ends.
+      if (elect_one()) {
+        tma_prefetch_desc(&tmap_q);
+        tma_prefetch_desc(&tmap_k);
+        tma_prefetch_desc(&tmap_v);
+        tma_prefetch_desc(&tmap_o);
+      }
+      bool ok = true;
+      int it = 0, n = 0;
+      auto load_kv = [&](const CUtensorMap* map, int row, int h, int b) {
+        const int slot = slot_of(it);
+        const int use = it / kKVSlots;
+        if (use > 0 && ok)
+          ok = wait_bar_warp(smem_u32(&sm.kv_empty[slot]), (use - 1) & 1, watch, kWaitKVEmpty);
+        if (ok) {
+          if (elect_one()) {
+            const uint32_t bar = smem_u32(&sm.kv_full[slot]);
+            mbar_arrive_expect_tx(bar, kTileBytes);
+            tma_load_4d(smem_u32(sm.kv[slot]), map, bar, 0, row, h, b);
+          }
+          ++it;
         }
-        ++it;
-      }
-    };
-    if (elect_one()) {
-      const uint32_t bar = smem_u32(&sm.q_full);
-      mbar_arrive_expect_tx(bar, kTileBytes);
-      tma_load_4d(smem_u32(sm.q), &tmap_q, bar, 0, q_row, h, b);
-    }
-    for (int j = 0; j < ns && ok; ++j) {
-      load_kv(&tmap_k, j);
-      load_kv(&tmap_v, j);
-    }
-    if (sm.abort && lane == 0) {
-      // leave no copy of ours in flight: wait (bounded) for every load still armed
-      for (int i = max(0, it - kKVSlots); i < it; ++i)
-        wait_bar(smem_u32(&sm.kv_full[slot_of(i)]), par_of(i), watch, kWaitDrain,
-                 20ull * 1000 * 1000, false);
-      wait_bar(smem_u32(&sm.q_full), 0, watch, kWaitDrain, 20ull * 1000 * 1000, false);
-    }
-    __syncwarp();
-  } else if (warp == kMmaWarp) {
-    // =================================================================== tcgen05 issuer
-    constexpr uint32_t idesc_s = make_idesc_bf16(kBlockM, kBlockN, false);
-    constexpr uint32_t idesc_o = make_idesc_bf16(kBlockM, kHeadDim, true);
-    const uint64_t desc_q = make_sw128_desc(smem_u32(sm.q));
-    const uint32_t t_s = tmem_base + kTmemS;
-    const uint32_t t_p = tmem_base + kTmemP;
-    const uint32_t t_o = tmem_base + kTmemO;
-    const uint32_t bar_s_full = smem_u32(&sm.s_full);
-    const uint32_t bar_o_full = smem_u32(&sm.o_full);
-
-    // S = Q K^T from ring slot `slot`, then release that slot
-    auto issue_s = [&](int slot) {
-      if (elect_one()) {
-        const uint64_t dk = make_sw128_desc(smem_u32(sm.kv[slot]));
-#pragma unroll
-        for (int kk = 0; kk < kHeadDim / 16; ++kk)  // +32 bytes along the row per K=16 step
-          umma_ss(t_s, desc_q + 2 * kk, dk + 2 * kk, idesc_s, kk > 0);
-        tc_commit(bar_s_full);
-        tc_commit(smem_u32(&sm.kv_empty[slot]));
-      }
-      __syncwarp();
-    };
-    auto issue_pv = [&](int slot, bool first) {
-      if (elect_one()) {
-        const uint64_t dv = make_sw128_desc(smem_u32(sm.kv[slot]));
-#pragma unroll
-        for (int kk = 0; kk < kBlockN / 16; ++kk)  // 16 V rows = 2048 bytes; 16 P values = 8 columns
-          umma_ts(t_o, t_p + 8 * kk, dv + 128 * kk, idesc_o, (!first) || kk > 0);
-        tc_commit(bar_o_full);
-        tc_commit(smem_u32(&sm.kv_empty[slot]));
-      }
-      __syncwarp();
-    };
-
-    bool ok = wait_bar_warp(smem_u32(&sm.q_full), 0, watch, kWaitQFull) &&
-              wait_bar_warp(smem_u32(&sm.kv_full[0]), 0, watch, kWaitKVFull);
-    if (ok) {
-      tc_fence_after();
-      issue_s(0);
-    }
-    for (int j = 0; j < ns && ok; ++j) {
-      const int itv = 2 * j + 1, itk = 2 * j + 2;
-      // ---- S for the next K tile, as soon as the softmax warps hold S(j) in registers
-      if (j + 1 < ns) {
-        FA_TRACE_EVENT(2, j, 0);
-        ok = wait_bar_warp(smem_u32(&sm.kv_full[slot_of(itk)]), par_of(itk), watch, kWaitKVFull) &&
-             wait_bar_warp(smem_u32(&sm.s_free), j & 1, watch, kWaitSFree);
+      };
+      const int item_stride = kPersistent ? static_cast<int>(gridDim.x) : p.n_items;
+      for (int item = blockIdx.x; item < p.n_items && ok; item += item_stride, ++n) {
+        const Item w = decode(item);
+        if (n > 0) ok = wait_bar_warp(smem_u32(&sm.q_empty), (n - 1) & 1, watch, kWaitQEmpty);
         if (!ok) break;
-        FA_TRACE_EVENT(2, j, 1);
-        tc_fence_after();
-        issue_s(slot_of(itk));
-        FA_TRACE_EVENT(2, j, 2);
+        if (elect_one()) {
+          const uint32_t bar = smem_u32(&sm.q_full);
+          mbar_arrive_expect_tx(bar, kTileBytes);
+          tma_load_4d(smem_u32(sm.q), &tmap_q, bar, 0, w.q_row, w.h, w.b);
+        }
+        for (int j = 0; j < w.ns && ok; ++j) {
+          load_kv(&tmap_k, j * kBlockN, w.h, w.b);
+          load_kv(&tmap_v, j * kBlockN, w.h, w.b);
+        }
       }
-      // ---- O += P V for this tile
-      FA_TRACE_EVENT(2, j, 3);
-      ok = wait_bar_warp(smem_u32(&sm.kv_full[slot_of(itv)]), par_of(itv), watch, kWaitKVFull) &&
-           wait_bar_warp(smem_u32(&sm.p_full), j & 1, watch, kWaitPFull);
-      if (!ok) break;
-      FA_TRACE_EVENT(2, j, 4);
-      tc_fence_after();
-      issue_pv(slot_of(itv), j == 0);
-      FA_TRACE_EVENT(2, j, 5);
+      if (sm.abort && lane == 0) {
+        // leave no copy of ours in flight: wait (bounded) for every load still armed
+        for (int i = max(0, it - kKVSlots); i < it; ++i)
+          wait_bar(smem_u32(&sm.kv_full[slot_of(i)]), par_of(i), watch, kWaitDrain,
+                   20ull * 1000 * 1000, false);
+        if (n > 0)
+          wait_bar(smem_u32(&sm.q_full), (n - 1) & 1, watch, kWaitDrain, 20ull * 1000 * 1000, false);
+      }
+      __syncwarp();
+    } else if (warp == kMmaWarp) {
+      // ================================================================= tcgen05 issuer
+      constexpr uint32_t idesc_s = make_idesc_bf16(kBlockM, kBlockN, false);
+      constexpr uint32_t idesc_o = make_idesc_bf16(kBlockM, kHeadDim, true);
+      const uint64_t desc_q = make_sw128_desc(smem_u32(sm.q));
+      const uint32_t t_s = tmem_base + kTmemS;
+      const uint32_t t_p = tmem_base + kTmemP;
+      const uint32_t t_o = tmem_base + kTmemO;
+      const uint32_t bar_s_full = smem_u32(&sm.s_full);
+      const uint32_t bar_o_full = smem_u32(&sm.o_full);
+
+      // S = Q K^T from ring slot `slot`; releases that slot, and the Q slot after an item's last S
+      auto issue_s = [&](int slot, bool last_of_item) {
+        if (elect_one()) {
+          const uint64_t dk = make_sw128_desc(smem_u32(sm.kv[slot]));
+#pragma unroll
+          for (int kk = 0; kk < kHeadDim / 16; ++kk)  // +32 bytes along the row per K=16 step
+            umma_ss(t_s, desc_q + 2 * kk, dk + 2 * kk, idesc_s, kk > 0);
+          tc_commit(bar_s_full);
+          tc_commit(smem_u32(&sm.kv_empty[slot]));
+          if (last_of_item) tc_commit(smem_u32(&sm.q_empty));
+        }
+        __syncwarp();
+      };
+      auto issue_pv = [&](int slot, bool first) {
+        if (elect_one()) {
+          const uint64_t dv = make_sw128_desc(smem_u32(sm.kv[slot]));
+#pragma unroll
+          for (int kk = 0; kk < kBlockN / 16; ++kk)  // 16 V rows = 2048 bytes; 16 P values = 8 columns
+            umma_ts(t_o, t_p + 8 * kk, dv + 128 * kk, idesc_o, (!first) || kk > 0);
+          tc_commit(bar_o_full);
+          tc_commit(smem_u32(&sm.kv_empty[slot]));
+        }
+        __syncwarp();
+      };
+
+      // Running counters: `it` = ring index of the next V to consume, `g` = global index of the
+      // tile whose PV comes next, `n` = local item index.
+      bool ok = true;
+      int it = 1, g = 0, n = 0;
+      int item = blockIdx.x;
+      Item w = decode(item < p.n_items ? item : 0);
+      if (item < p.n_items) {
+        ok = wait_bar_warp(smem_u32(&sm.q_full), 0, watch, kWaitQFull) &&
+             wait_bar_warp(smem_u32(&sm.kv_full[0]), 0, watch, kWaitKVFull);
+        if (ok) {
+          tc_fence_after();
+          issue_s(0, w.ns == 1);
+        }
+      }
+      const int item_stride = kPersistent ? static_cast<int>(gridDim.x) : p.n_items;
+      for (; item < p.n_items && ok; item += item_stride, ++n) {
+        const int next_item = item + item_stride;
+        const bool has_next_item = kPersistent && next_item < p.n_items;
+        const Item wn = decode(has_next_item ? next_item : item);
+        for (int j = 0; j < w.ns && ok; ++j, ++g) {
+          const int itv = it;          // V_j of this item
+          const int itk = it + 1;      // the next K in ring order: K_{j+1}, or K_0 of the next item
+          const bool last = j + 1 == w.ns;
+          // ---- S for the next tile, as soon as the softmax warps hold S(g) in registers
+          if (!last || has_next_item) {
+            if (last)   // the next item's Q must have landed (its load waited for q_empty)
+              ok = wait_bar_warp(smem_u32(&sm.q_full), (n + 1) & 1, watch, kWaitQFull);
+            ok = ok &&
+                 wait_bar_warp(smem_u32(&sm.kv_full[slot_of(itk)]), par_of(itk), watch, kWaitKVFull) &&
+                 wait_bar_warp(smem_u32(&sm.s_free), g & 1, watch, kWaitSFree);
+            if (!ok) break;
+            tc_fence_after();
+            issue_s(slot_of(itk), last ? wn.ns == 1 : j + 2 == w.ns);
+          }
+          // ---- O += P V for this tile
+          ok = wait_bar_warp(smem_u32(&sm.kv_full[slot_of(itv)]), par_of(itv), watch, kWaitKVFull) &&
+               wait_bar_warp(smem_u32(&sm.p_full), g & 1, watch, kWaitPFull);
+          if (ok && j == 0 && n > 0)   // the previous item's epilogue must have read O
+            ok = wait_bar_warp(smem_u32(&sm.o_free), (n - 1) & 1, watch, kWaitOFree);
+          if (!ok) break;
+          tc_fence_after();
+          issue_pv(slot_of(itv), j == 0);
+          it += 2;
+        }
+        w = wn;
+      }
     }
   } else {
     // =================================================================== softmax warps
+    reg_alloc<kSoftmaxRegs>();      // executed by all four warps of warpgroup 0
     const int r = threadIdx.x;                  // row inside the tile == TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
     const uint32_t t_s = tmem_base + lane_base + kTmemS;
@@ -301,142 +376,197 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     const uint32_t bar_s_free = smem_u32(&sm.s_free);
     const uint32_t bar_p = smem_u32(&sm.p_full);
     const uint32_t bar_o = smem_u32(&sm.o_full);
+    const uint32_t bar_o_free = smem_u32(&sm.o_free);
+    const uint32_t bar_o_staged = smem_u32(&sm.o_staged);
+    const uint32_t bar_stage_free = smem_u32(&sm.stage_free);
+    // this thread's row of the staging tile; 16-byte chunk c goes to position c ^ (r & 7)
+    // (the 128-byte swizzle the TMA store expects)
+    const uint32_t stage_row = smem_u32(sm.o_stage) + r * 128;
     constexpr uint32_t kNegInf = 0xff800000u;
-#ifdef FA_TRACE
-    const bool tracer = r == 0;
-#endif
 
-    float m_ref = -CUDART_INF_F;  // max the exponentials are currently taken against (raw scores)
-    float l = 0.f;                // running sum of exp2((s - m_ref) * c)
     bool ok = true;
+    int g = 0;   // running tile counter across work items (selects the barrier phases)
+    int n = 0;   // local work-item counter
 
-    for (int j = 0; j < ns; ++j) {
-#ifdef FA_TRACE
-      if (tracer) FA_TRACE_EVENT(0, j, 0);
-#endif
-      ok = wait_bar_warp(bar_s_full, j & 1, watch, kWaitSFull);
-      if (!ok) break;
+    // A finished item whose epilogue is still owed.  It is run in the middle of the NEXT item's
+    // first tile (after that tile's P is stored, before the issuer is told about it): by then the
+    // last O += P V of the finished item has long completed, so nobody sits waiting for it.
+    bool owed = false;
+    int owed_q_row = 0, owed_h = 0, owed_b = 0, owed_n = 0;
+    float owed_m = 0.f, owed_l = 1.f;
+
+    // O / l -> bf16 -> swizzled staging tile -> TMA store; LSE.  Reads O of the owed item.
+    auto epilogue = [&]() -> bool {
       tc_fence_after();
-      uint32_t sv[kBlockN];
-      tmem_ld_x128(t_s, sv);
-      // S is in registers: let the issuer overwrite it with the next tile's scores
+      uint32_t ov[kHeadDim];
+      tmem_ld_x64(t_o, ov);
+      // O is in registers: the issuer may start the next item's accumulation
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_s_free);
+      if (lane == 0) mbar_arrive(bar_o_free);
+      // The staging tile is free once the previous item's TMA store has read it.  The thread
+      // that issued that store waits for it and tells the others.
+      if (owed_n > 0) {
+        if (threadIdx.x == 0) {
+          tma_store_wait_read<0>();
+          mbar_arrive(bar_stage_free);
+        }
+        if (!wait_bar_warp(bar_stage_free, (owed_n - 1) & 1, watch, kWaitStageFree)) return false;
+      }
+      const float inv_l = 1.0f / owed_l;
+#pragma unroll
+      for (int ck = 0; ck < 8; ++ck) {
+        uint4 wv;
+        wv.x = pack_bf16(__uint_as_float(ov[8 * ck + 0]) * inv_l, __uint_as_float(ov[8 * ck + 1]) * inv_l);
+        wv.y = pack_bf16(__uint_as_float(ov[8 * ck + 2]) * inv_l, __uint_as_float(ov[8 * ck + 3]) * inv_l);
+        wv.z = pack_bf16(__uint_as_float(ov[8 * ck + 4]) * inv_l, __uint_as_float(ov[8 * ck + 5]) * inv_l);
+        wv.w = pack_bf16(__uint_as_float(ov[8 * ck + 6]) * inv_l, __uint_as_float(ov[8 * ck + 7]) * inv_l);
+        st_shared_v4(stage_row + ((ck ^ (r & 7)) << 4), wv);
+      }
+      fence_proxy_async_smem();     // generic-proxy writes -> visible to the TMA engine
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_o_staged);
+      bool good = true;
+      if (warp == 0) {
+        good = wait_bar_warp(bar_o_staged, owed_n & 1, watch, kWaitOStaged);
+        if (good && lane == 0) {    // rows >= N are clipped by the tensor map
+          tma_store_4d(&tmap_o, smem_u32(sm.o_stage), 0, owed_q_row, owed_h, owed_b);
+          tma_store_commit();
+        }
+        __syncwarp();
+      }
+      const int row = owed_q_row + r;
+      if (p.lse != nullptr && row < p.N) {
+        // ln(sum_j exp(scale * s_j)) = ln2 * (m_ref * c + log2(l))
+        p.lse[((long long)owed_b * p.H + owed_h) * p.N + row] =
+            0.6931471805599453f * (owed_m * c + log2f(owed_l));
+      }
+      owed = false;
+      return good;
+    };
 
-      const int col0 = j * kBlockN;
-      if (p.causal) {
-        if (col0 == q_row) {  // the diagonal tile: column k is visible to row r iff k <= r
+    const int item_stride = kPersistent ? static_cast<int>(gridDim.x) : p.n_items;
+    for (int item = blockIdx.x; item < p.n_items && ok; item += item_stride, ++n) {
+      const Item w = decode(item);
+      float m_ref = -CUDART_INF_F;  // max the exponentials are currently taken against (raw scores)
+      float l = 0.f;                // running sum of exp2((s - m_ref) * c)
+
+      for (int j = 0; j < w.ns; ++j, ++g) {
+        ok = wait_bar_warp(bar_s_full, g & 1, watch, kWaitSFull);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t sv[kBlockN];
+        {  // two 64-column loads: a single 128-register instruction does not fit the 128-register
+           // launch allocation the assembler plans with, whatever setmaxnreg grants later
+          uint32_t (&lo)[64] = *reinterpret_cast<uint32_t (*)[64]>(&sv[0]);
+          uint32_t (&hi)[64] = *reinterpret_cast<uint32_t (*)[64]>(&sv[64]);
+          tmem_ld_nowait_x64(t_s, lo);
+          tmem_ld_nowait_x64(t_s + 64, hi);
+          tmem_wait_ld_fence(sv);
+        }
+        // S is in registers: let the issuer overwrite it with the next tile's scores
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_s_free);
+
+        const int col0 = j * kBlockN;
+        if (p.causal) {
+          if (col0 == w.q_row) {  // the diagonal tile: column k is visible to row r iff k <= r
+#pragma unroll
+            for (int k = 0; k < kBlockN; ++k)
+              if (k > r) sv[k] = kNegInf;
+          }
+        } else if (col0 + kBlockN > p.N) {  // ragged last tile: TMA zero-fill gives score 0, not -inf
+          const int lim = p.N - col0;
 #pragma unroll
           for (int k = 0; k < kBlockN; ++k)
-            if (k > r) sv[k] = kNegInf;
+            if (k >= lim) sv[k] = kNegInf;
         }
-      } else if (col0 + kBlockN > p.N) {  // ragged last tile: TMA zero-fill gives score 0, not -inf
-        const int lim = p.N - col0;
-#pragma unroll
-        for (int k = 0; k < kBlockN; ++k)
-          if (k >= lim) sv[k] = kNegInf;
-      }
 
-      float mx[4];
+        float mx[4];
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {   // four independent chains of 32
-        const int o = 32 * ch;
-        float m = fmax3(__uint_as_float(sv[o]), __uint_as_float(sv[o + 1]), __uint_as_float(sv[o + 2]));
+        for (int ch = 0; ch < 4; ++ch) {   // four independent chains of 32
+          const int o = 32 * ch;
+          float m = fmax3(__uint_as_float(sv[o]), __uint_as_float(sv[o + 1]), __uint_as_float(sv[o + 2]));
 #pragma unroll
-        for (int k = 3; k + 1 < 32; k += 2)
-          m = fmax3(m, __uint_as_float(sv[o + k]), __uint_as_float(sv[o + k + 1]));
-        mx[ch] = fmaxf(m, __uint_as_float(sv[o + 31]));
-      }
-      const float m_new = fmaxf(fmax3(mx[0], mx[1], mx[2]), fmaxf(mx[3], m_ref));
-
-      if (j == 0) {
-        m_ref = m_new;
-      } else {
-        // O += P V of the previous tile must be finished before P is overwritten or O is touched
-        ok = wait_bar_warp(bar_o, (j - 1) & 1, watch, kWaitOFull);
-        if (!ok) break;
-        // Rescale lazily: while the max grew by less than 2^8 keep the old reference; P stays
-        // below 256 and the final O / l is exact because O, l and P share one reference.
-        const bool need = (m_new - m_ref) * c > kRescaleThresholdLog2;
-        if (__any_sync(0xffffffffu, need)) {
-          const float f = need ? ex2_approx((m_ref - m_new) * c) : 1.0f;
-          tc_fence_after();
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            uint32_t ov[32];
-            tmem_ld_x32(t_o + 32 * half, ov);
-#pragma unroll
-            for (int k = 0; k < 32; ++k) ov[k] = __float_as_uint(__uint_as_float(ov[k]) * f);
-            tmem_st_x32(t_o + 32 * half, ov);
-          }
-          l *= f;
-          if (need) m_ref = m_new;
+          for (int k = 3; k + 1 < 32; k += 2)
+            m = fmax3(m, __uint_as_float(sv[o + k]), __uint_as_float(sv[o + k + 1]));
+          mx[ch] = fmaxf(m, __uint_as_float(sv[o + 31]));
         }
-      }
-#ifdef FA_TRACE
-      if (tracer) FA_TRACE_EVENT(0, j, 1);
-#endif
+        const float m_new = fmaxf(fmax3(mx[0], mx[1], mx[2]), fmaxf(mx[3], m_ref));
 
-      const float neg_mc = -m_ref * c;
-      float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-#pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {   // 32 scores -> 16 packed registers -> one TMEM store
-        uint32_t pk[16];
-#pragma unroll
-        for (int k = 0; k < 32; k += 4) {
-          const int o = 32 * ch + k;
-          const float p0 = ex2_approx(fmaf(__uint_as_float(sv[o + 0]), c, neg_mc));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(sv[o + 1]), c, neg_mc));
-          const float p2 = ex2_approx(fmaf(__uint_as_float(sv[o + 2]), c, neg_mc));
-          const float p3 = ex2_approx(fmaf(__uint_as_float(sv[o + 3]), c, neg_mc));
-          l0 += p0; l1 += p1; l2 += p2; l3 += p3;
-          pk[k / 2 + 0] = pack_bf16(p0, p1);
-          pk[k / 2 + 1] = pack_bf16(p2, p3);
+        // O += P V of the previous tile (of this or the previous item) must be finished before P
+        // is overwritten or O is touched
+        if (g > 0) {
+          ok = wait_bar_warp(bar_o, (g - 1) & 1, watch, kWaitOFull);
+          if (!ok) break;
         }
-        tmem_st_x16(t_p + 16 * ch, pk);
-      }
-      l += (l0 + l1) + (l2 + l3);
-#ifdef FA_TRACE
-      if (tracer) FA_TRACE_EVENT(0, j, 2);
-#endif
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_p);
-    }
-
-    // ---- epilogue: O / l -> bf16, LSE
-    if (ok) {
-      ok = wait_bar_warp(bar_o, (ns - 1) & 1, watch, kWaitOFull);
-      if (ok) {
-        tc_fence_after();
-        const int row = q_row + r;
-        const float inv_l = 1.0f / l;
-        __nv_bfloat16* orow = p.o + (long long)b * p.o_sb + (long long)h * p.o_sh +
-                              (long long)row * p.o_sn;
+        if (j == 0) {
+          m_ref = m_new;
+        } else {
+          // Rescale lazily: while the max grew by less than 2^8 keep the old reference; P stays
+          // below 256 and the final O / l is exact because O, l and P share one reference.
+          const bool need = (m_new - m_ref) * c > kRescaleThresholdLog2;
+          if (__any_sync(0xffffffffu, need)) {
+            const float f = need ? ex2_approx((m_ref - m_new) * c) : 1.0f;
+            tc_fence_after();
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t ov[32];
-          tmem_ld_x32(t_o + 32 * half, ov);
-          if (row < p.N) {
+            for (int half = 0; half < 2; ++half) {
+              uint32_t ov[32];
+              tmem_ld_x32(t_o + 32 * half, ov);
 #pragma unroll
-            for (int k = 0; k < 32; k += 8) {
-              uint4 w;
-              w.x = pack_bf16(__uint_as_float(ov[k + 0]) * inv_l, __uint_as_float(ov[k + 1]) * inv_l);
-              w.y = pack_bf16(__uint_as_float(ov[k + 2]) * inv_l, __uint_as_float(ov[k + 3]) * inv_l);
-              w.z = pack_bf16(__uint_as_float(ov[k + 4]) * inv_l, __uint_as_float(ov[k + 5]) * inv_l);
-              w.w = pack_bf16(__uint_as_float(ov[k + 6]) * inv_l, __uint_as_float(ov[k + 7]) * inv_l);
-              *reinterpret_cast<uint4*>(orow + 32 * half + k) = w;
+              for (int k = 0; k < 32; ++k) ov[k] = __float_as_uint(__uint_as_float(ov[k]) * f);
+              tmem_st_x32(t_o + 32 * half, ov);
             }
+            l *= f;
+            if (need) m_ref = m_new;
           }
         }
-        if (p.lse != nullptr && row < p.N) {
-          // ln(sum_j exp(scale * s_j)) = ln2 * (m_ref * c + log2(l))
-          p.lse[((long long)b * p.H + h) * p.N + row] = 0.6931471805599453f * (m_ref * c + log2f(l));
+
+        const float neg_mc = -m_ref * c;
+        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {   // 32 scores -> 16 packed registers -> one TMEM store
+          uint32_t pk[16];
+#pragma unroll
+          for (int k = 0; k < 32; k += 4) {
+            const int o = 32 * ch + k;
+            const float p0 = ex2_approx(fmaf(__uint_as_float(sv[o + 0]), c, neg_mc));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(sv[o + 1]), c, neg_mc));
+            const float p2 = ex2_approx(fmaf(__uint_as_float(sv[o + 2]), c, neg_mc));
+            const float p3 = ex2_approx(fmaf(__uint_as_float(sv[o + 3]), c, neg_mc));
+            l0 += p0; l1 += p1; l2 += p2; l3 += p3;
+            pk[k / 2 + 0] = pack_bf16(p0, p1);
+            pk[k / 2 + 1] = pack_bf16(p2, p3);
+          }
+          tmem_st_x16(t_p + 16 * ch, pk);
         }
+        l += (l0 + l1) + (l2 + l3);
+        tmem_wait_st();
+
+        // the epilogue owed to the previous item: its O is final (the wait above covered its last
+        // PV) and must be read before the issuer accumulates this item's first P V into O
+        if (kPersistent && owed) {
+          ok = epilogue();
+          if (!ok) break;
+        }
+
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_p);
       }
+      if (!ok) break;
+      owed = true;
+      owed_q_row = w.q_row; owed_h = w.h; owed_b = w.b; owed_n = n;
+      owed_m = m_ref; owed_l = l;
     }
+    // the last item's epilogue
+    if (ok && owed) {
+      ok = wait_bar_warp(bar_o, (g - 1) & 1, watch, kWaitOFull);
+      if (ok) ok = epilogue();
+    }
+    // the last TMA store must have read the staging tile before shared memory goes away
+    if (threadIdx.x == 0) tma_store_wait_read<0>();
   }
 
   // ---- teardown: every TMEM access above is complete (loads waited, MMAs observed via o_full)
