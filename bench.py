@@ -345,25 +345,31 @@ def main():
     prefill = []
     if not args.no_sweep:
         from tfg_flashattention_b200 import gpt2
-        for name, batch, seed, steps in (("gpt2-small", 8, 1, 5), ("gpt2-xl", 32, 3, 3)):
+        for name, batch, seed, steps in (("gpt2-small", 8, 1, 7), ("gpt2-xl", 32, 3, 5)):
             cfg = gpt2.gpt2_config(name, impl_type="cuda")
             model = gpt2.init_random(gpt2.GPTModel(cfg, dtype=torch.bfloat16), seed=seed).cuda().eval()
+            model.prepare_for_inference()     # fused QKV GEMM, vocabulary padded to a multiple of 64
             ids = torch.randint(0, cfg["vocab_size"], (batch, 1024),
                                 generator=torch.Generator().manual_seed(seed + rank)).cuda()
             with torch.no_grad():
-                for _ in range(2):
+                for _ in range(3):
                     model(ids)
                 barrier(world)
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record()
-                for _ in range(steps):
+                # one event pair per forward; the median is robust against a first-use stall
+                # (cuBLAS kernel loading, allocator growth) landing inside the timed steps
+                evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                       for _ in range(steps)]
+                for e0, e1 in evs:
+                    e0.record()
                     logits = model(ids)
-                e1.record()
+                    e1.record()
                 barrier(world)
-            pms = max_over_ranks(e0.elapsed_time(e1) / steps, world)
+            times = [e0.elapsed_time(e1) for e0, e1 in evs]
+            pms = max_over_ranks(statistics.median(times), world)
+            pms_mean = max_over_ranks(sum(times) / len(times), world)
             tok_s = world * batch * 1024 / (pms * 1e-3)
             prefill.append({"model": name, "batch_per_gpu": batch, "seq_len": 1024, "dtype": "bf16",
-                            "weights": f"random N(0,0.02) seed {seed}", "ms_per_forward": round(pms, 3),
+                            "weights": f"random N(0,0.02) seed {seed}", "ms_per_forward": round(pms, 3), "ms_per_forward_mean": round(pms_mean, 3), "timing": f"median of {steps} forwards, CUDA events",
                             "tokens_per_s": round(tok_s, 1),
                             "model_tflops_per_gpu": round(tok_s / world * gpt2.prefill_flops_per_token(cfg, 1024) / 1e12, 1),
                             "attention": "fa::fa_fwd_kernel on strided [B,N,H,d] views, every layer",

@@ -34,6 +34,19 @@ def test_last_token_only(golden_dir):
     torch.testing.assert_close(last, logits_ref[:, -1:, :], rtol=1e-4, atol=2e-5)
 
 
+def test_prepare_for_inference_is_a_pure_cache(golden_dir):
+    """Fused QKV + padded head give the same logits and leave the state_dict untouched."""
+    model, ids, logits_ref = _load_tiny(golden_dir, "manual")
+    keys = sorted(model.state_dict().keys())
+    model.prepare_for_inference()
+    assert sorted(model.state_dict().keys()) == keys
+    assert model._head_w is not None and model._head_w.shape[0] % 64 == 0   # vocab 97 -> 128
+    with torch.no_grad():
+        logits = model(ids)
+    assert logits.shape == logits_ref.shape
+    torch.testing.assert_close(logits, logits_ref, rtol=1e-4, atol=2e-5)
+
+
 def test_configs_and_flops():
     cfg = gpt2.gpt2_config("gpt2-xl")
     assert (cfg["emb_dim"], cfg["n_layers"], cfg["n_heads"]) == (1600, 48, 25)
@@ -69,6 +82,7 @@ def test_bf16_model_prefill_small(fa_lib):
     cfg = gpt2.gpt2_config("gpt2-small")
     cfg["n_layers"] = 2
     m = gpt2.init_random(gpt2.GPTModel(cfg, dtype=torch.bfloat16), seed=1).cuda().eval()
+    m.prepare_for_inference()
     ids = torch.randint(0, cfg["vocab_size"], (2, 1024), generator=torch.Generator().manual_seed(1)).cuda()
     with torch.no_grad():
         a = m(ids).float()

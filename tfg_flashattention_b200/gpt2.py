@@ -20,6 +20,12 @@ What differs, on purpose:
     which scrambles heads and tokens.  Parity is defined against the "manual" branch, so the
     transpose is applied here.
   * LayerNorm and GELU call the fused torch ops (same arithmetic, one kernel each).
+  * `prepare_for_inference()` builds two derived, cached tensors without touching the parameters
+    (so state_dicts stay interchangeable): the three QKV projections concatenated into one
+    `[3*d_model, d_model]` weight (one GEMM instead of three; q, k, v become column slices of one
+    buffer, which the kernel reads in place), and the output head padded from 50257 to a
+    multiple of 64 rows (an odd vocabulary size sends the logits GEMM down a slow unaligned
+    cuBLAS path); the padded logits are sliced back to the vocabulary size.
   * `GPTModel(cfg, dtype=torch.bfloat16)` builds the whole model in bf16 (the prefill benchmark
     configuration); the default keeps the reference's precision recipe: fp32 everywhere, bf16
     autocast around attention only (:153-154).
@@ -62,13 +68,26 @@ class MultiHeadAttention(nn.Module):
         self.out_proj = nn.Linear(d_out, d_out)
         self.dropout = nn.Dropout(dropout)
         self.context_length = context_length
+        self._qkv_w = None      # fused [3*d_out, d_in] weight / [3*d_out] bias (inference cache)
+        self._qkv_b = None
+
+    def fuse_qkv(self):
+        """Cache the concatenated projection (call again after changing the weights)."""
+        with torch.no_grad():
+            self._qkv_w = torch.cat([self.W_query.weight, self.W_key.weight, self.W_value.weight], 0).contiguous()
+            self._qkv_b = (None if self.W_query.bias is None else
+                           torch.cat([self.W_query.bias, self.W_key.bias, self.W_value.bias], 0).contiguous())
 
     def forward(self, x):
         b, n, _ = x.shape
         h, d = self.num_heads, self.head_dim
-        q = self.W_query(x).view(b, n, h, d).transpose(1, 2)
-        k = self.W_key(x).view(b, n, h, d).transpose(1, 2)
-        v = self.W_value(x).view(b, n, h, d).transpose(1, 2)
+        if self._qkv_w is not None and not self.training:
+            qkv = F.linear(x, self._qkv_w, self._qkv_b).view(b, n, 3, h, d)
+            q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+        else:
+            q = self.W_query(x).view(b, n, h, d).transpose(1, 2)
+            k = self.W_key(x).view(b, n, h, d).transpose(1, 2)
+            v = self.W_value(x).view(b, n, h, d).transpose(1, 2)
         if self.impl_type == "cuda":
             from . import custom_flash_attn
             if q.dtype != torch.bfloat16:      # outside autocast: the kernel is bf16-only
@@ -152,8 +171,20 @@ class GPTModel(nn.Module):
         self.trf_blocks = nn.Sequential(*[TransformerBlock(cfg) for _ in range(cfg["n_layers"])])
         self.final_norm = LayerNorm(cfg)
         self.out_head = nn.Linear(cfg["emb_dim"], cfg["vocab_size"], bias=False)
+        self._head_w = None     # out_head weight padded to a multiple of 64 rows (inference cache)
         if dtype is not None:
             self.to(dtype)
+
+    def prepare_for_inference(self):
+        """Build the fused QKV weights and the padded output head (derived caches; parameters and
+        state_dict are untouched).  Call after loading or moving the weights."""
+        for blk in self.trf_blocks:
+            blk.att.fuse_qkv()
+        w = self.out_head.weight
+        pad = (-w.shape[0]) % 64
+        with torch.no_grad():
+            self._head_w = F.pad(w, (0, 0, 0, pad)).contiguous() if pad else None
+        return self
 
     def forward(self, in_idx, last_token_only=False):
         _, n = in_idx.shape
@@ -162,6 +193,8 @@ class GPTModel(nn.Module):
         x = self.final_norm(x)
         if last_token_only:           # what generate() consumes (model_inference.py:206)
             x = x[:, -1:, :]
+        if self._head_w is not None and not self.training:
+            return F.linear(x, self._head_w)[..., :self.out_head.weight.shape[0]]
         return self.out_head(x)
 
 
