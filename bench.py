@@ -45,6 +45,7 @@ UNIT = "TFLOP/s"
 # dram__bytes_write.sum).  Captured with ncu at B=12 (118.04 + 20.30 MB per launch) and scaled by
 # 32/12 to the benchmark's B=32: every (batch, head) is independent, so traffic grows in proportion.
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 138.34e6 * 32 / 12
+E2E_CHUNKS = 8                # batch slices the host-buffer call pipelines through PCIe
 CPU_SAMPLE_BATCH = 4          # batch entries (x25 heads) the CPU legs compute per repetition
 
 
@@ -176,19 +177,17 @@ def time_kernel(cfa, q, k, v, causal, steps, warmup, world):
 
 
 def time_e2e(cfa, w, rank, steps, warmup, world):
-    """ms per step through the public call with HOST buffers: pinned q, k, v -> device, forward,
-    O -> pinned host, all inside the timed region."""
+    """ms per step through the public host-buffer call (custom_flash_attn.forward_host): pinned
+    q, k, v -> device, forward, O -> pinned host, all inside the timed region; the call cuts the
+    batch into slices so that uploads, kernels and downloads overlap."""
     qd, kd, vd = device_inputs(w, rank)
     hq, hk, hv = (t.cpu().pin_memory() for t in (qd, kd, vd))
     ho = torch.empty_like(hq).pin_memory()
     del qd, kd, vd
 
     def step():
-        q = hq.to("cuda", non_blocking=True)
-        k = hk.to("cuda", non_blocking=True)
-        v = hv.to("cuda", non_blocking=True)
-        o = cfa.forward(q, k, v)
-        ho.copy_(o, non_blocking=True)
+        # the public host-buffer call: chunked upload / kernel / download pipeline
+        cfa.forward_host(hq, hk, hv, out=ho, chunks=E2E_CHUNKS)
 
     for _ in range(max(1, warmup)):
         step()

@@ -186,6 +186,27 @@ def test_long_context_stress_rows(cfa):
         assert ((lse[0, h, rows].cpu() - rlb).abs() <= 1e-3 * rlb.abs().clamp_min(1.0)).all()
 
 
+@pytest.mark.parametrize("causal", [True, False])
+def test_extreme_score_jumps(cfa, causal):
+    """Key rows scaled x64 push some scores ~2^90 (in exp2 units) above everything seen before
+    them: the running-max rescale of O and l must keep the result finite and equal to the oracle.
+    Covers huge keys late in the sequence, early in it, and a single huge key on a tile boundary."""
+    torch.manual_seed(77)
+    N = 640
+    for big_rows in (slice(400, 420), slice(3, 9), slice(128, 129)):
+        q, k, v = (torch.randn(1, 2, N, 64) for _ in range(3))
+        k[:, :, big_rows] *= 64.0
+        qb, kb, vb = (t.to("cuda", torch.bfloat16) for t in (q, k, v))
+        o, lse = cfa.forward(qb, kb, vb, causal=causal, return_lse=True)
+        assert cfa.last_status() == 0
+        assert torch.isfinite(o).all() and torch.isfinite(lse).all()
+        ro, rl = _oracle().manual_attention(qb.float().cpu(), kb.float().cpu(), vb.float().cpu(),
+                                            causal=causal, return_lse=True)
+        d = (o.float().cpu() - ro).abs()
+        assert d.max().item() <= 3e-2 and d.mean().item() <= MEAN_ABS, (d.max().item(), d.mean().item())
+        assert ((lse.cpu() - rl).abs() <= 1e-3 * rl.abs().clamp_min(1.0)).all()
+
+
 def test_full_size_properties(cfa):
     """Size-independent properties at a full benchmark size (B=32, H=25, N=1024), where a CPU
     check of every head would take minutes: (i) heads are independent -- a head computed inside
@@ -227,6 +248,22 @@ def test_empty_and_error_paths(cfa):
     q = torch.zeros(1, 1, 8, 64, device="cuda", dtype=torch.bfloat16)
     with pytest.raises(RuntimeError, match="same shape"):
         cfa.forward(q, q[:, :, :4], q)
+
+
+def test_forward_host_pipeline_matches_device_call(cfa):
+    """Host-buffer entry: chunked upload / kernel / download pipeline, same bits as one call."""
+    torch.manual_seed(41)
+    q, k, v = (torch.randn(7, 3, 300, 64).bfloat16().pin_memory() for _ in range(3))
+    ref = cfa.forward(q.cuda(), k.cuda(), v.cuda()).cpu()
+    for chunks in (1, 2, 4, 16):
+        out = cfa.forward_host(q, k, v, chunks=chunks)
+        assert cfa.last_status() == 0
+        assert torch.equal(out, ref)
+    # reuse of a caller-provided pinned output, non-causal
+    out = torch.empty_like(q).pin_memory()
+    r = cfa.forward_host(q, k, v, out=out, causal=False, chunks=3)
+    assert r.data_ptr() == out.data_ptr()
+    assert torch.equal(out, cfa.forward(q.cuda(), k.cuda(), v.cuda(), causal=False).cpu())
 
 
 def test_non_default_stream(cfa):

@@ -29,7 +29,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["forward", "last_status"]
+__all__ = ["forward", "forward_host", "last_status"]
 
 
 def _check_input(t: torch.Tensor, name: str) -> None:
@@ -101,6 +101,80 @@ def forward(Q, K, V, causal=True, return_lse=False, softmax_scale=None, out=None
     if rc != 0:
         raise RuntimeError(f"custom_flash_attn.forward failed ({rc}): {_lib.strerror(rc)}")
     return (O, lse) if return_lse else O
+
+
+class _HostPipeline:
+    """Device-side chunk buffers and streams for forward_host, cached per (device, chunk shape)."""
+
+    def __init__(self, device, shape):
+        self.copy_in = torch.cuda.Stream(device)
+        self.copy_out = torch.cuda.Stream(device)
+        # two sets of chunk buffers: chunk i+1 is uploaded while chunk i is computed
+        self.bufs = [tuple(torch.empty(shape, dtype=torch.bfloat16, device=device) for _ in range(4))
+                     for _ in range(2)]
+
+
+_host_pipelines = {}
+
+
+def forward_host(Q, K, V, out=None, causal=True, softmax_scale=None, device=None, chunks=4):
+    """Attention forward for HOST-resident tensors: q, k, v [B,H,N,d] bf16 in (ideally pinned) host
+    memory, O returned in host memory (`out`, pinned, is reused when given).
+
+    The batch is cut into `chunks` slices that flow through a three-stage pipeline -- upload of
+    slice i+1, kernel on slice i, download of slice i-1 -- on separate CUDA streams, so the PCIe
+    transfers in both directions overlap each other and the kernel instead of running back to
+    back.  Returns after the last download has completed."""
+    for t, name in ((Q, "Q"), (K, "K_mat"), (V, "V")):
+        if t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 4:
+            raise RuntimeError(f"{name} must be a host bfloat16 tensor of shape [B, H, N, d]")
+    if K.shape != Q.shape or V.shape != Q.shape:
+        raise RuntimeError("Q, K_mat and V must have the same shape [B, H, N, d]")
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    B = Q.shape[0]
+    if out is None:
+        out = torch.empty(Q.shape, dtype=torch.bfloat16).pin_memory()
+    if B == 0 or Q.numel() == 0:
+        return out
+    chunks = max(1, min(int(chunks), B))
+    bounds = [(B * i) // chunks for i in range(chunks + 1)]
+    cmax = max(bounds[i + 1] - bounds[i] for i in range(chunks))
+    key = (dev.index, cmax) + tuple(Q.shape[1:])
+    pipe = _host_pipelines.get(key)
+    if pipe is None:
+        pipe = _host_pipelines[key] = _HostPipeline(dev, (cmax,) + tuple(Q.shape[1:]))
+    compute = torch.cuda.current_stream(dev)
+    pipe.copy_in.wait_stream(compute)
+    pipe.copy_out.wait_stream(compute)
+    computed = [None, None]      # event: kernel that used buffer set s has finished
+    downloaded = [None, None]    # event: O of buffer set s has been copied out
+    for i in range(chunks):
+        lo, hi = bounds[i], bounds[i + 1]
+        n = hi - lo
+        s = i & 1
+        dq, dk, dv, do = (b[:n] for b in pipe.bufs[s])
+        with torch.cuda.stream(pipe.copy_in):
+            if computed[s] is not None:
+                pipe.copy_in.wait_event(computed[s])      # q, k, v of this set are no longer read
+            dq.copy_(Q[lo:hi], non_blocking=True)
+            dk.copy_(K[lo:hi], non_blocking=True)
+            dv.copy_(V[lo:hi], non_blocking=True)
+            uploaded = torch.cuda.Event()
+            uploaded.record(pipe.copy_in)
+        compute.wait_event(uploaded)
+        if downloaded[s] is not None:
+            compute.wait_event(downloaded[s])              # O of this set has left the device
+        forward(dq, dk, dv, causal=causal, softmax_scale=softmax_scale, out=do)
+        computed[s] = torch.cuda.Event()
+        computed[s].record(compute)
+        with torch.cuda.stream(pipe.copy_out):
+            pipe.copy_out.wait_event(computed[s])
+            out[lo:hi].copy_(do, non_blocking=True)
+            downloaded[s] = torch.cuda.Event()
+            downloaded[s].record(pipe.copy_out)
+    compute.wait_stream(pipe.copy_out)
+    pipe.copy_out.synchronize()
+    return out
 
 
 def last_status(device=None) -> int:
