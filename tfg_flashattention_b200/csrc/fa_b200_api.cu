@@ -74,9 +74,11 @@ void init_device(int dev) {
   // The kernel moves registers between its warpgroups with setmaxnreg; that only works (and
   // otherwise blocks for ever) if the compiler gave the kernel the launch allocation the budget
   // in fa_fwd_sm100.cuh assumes.  Refuse to launch a build where it did not.
-  for (int variant = 0; variant < 2; ++variant) {
-    const void* fn = variant == 0 ? reinterpret_cast<const void*>(&fa::fa_fwd_kernel<false>)
-                                  : reinterpret_cast<const void*>(&fa::fa_fwd_kernel<true>);
+  const void* variants[4] = {reinterpret_cast<const void*>(&fa::fa_fwd_kernel<false, false>),
+                             reinterpret_cast<const void*>(&fa::fa_fwd_kernel<false, true>),
+                             reinterpret_cast<const void*>(&fa::fa_fwd_kernel<true, false>),
+                             reinterpret_cast<const void*>(&fa::fa_fwd_kernel<true, true>)};
+  for (const void* fn : variants) {
     cudaFuncAttributes fattr;
     e = cudaFuncGetAttributes(&fattr, fn);
     if (e != cudaSuccess) { st.init_error = static_cast<int>(e); return; }
@@ -182,6 +184,8 @@ int fa_b200_fwd(const fa_b200_params* p) {
   kp.H = p->H;
   kp.N = p->N;
   kp.n_qtiles = (p->N + fa::kBlockM - 1) / fa::kBlockM;
+  kp.div_qtiles = fa::make_fast_div(static_cast<uint32_t>(kp.n_qtiles));
+  kp.div_heads = fa::make_fast_div(static_cast<uint32_t>(p->H));
   kp.causal = p->causal ? 1 : 0;
   const float scale = p->softmax_scale > 0.0f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(p->d));
   kp.scale_log2 = scale * 1.4426950408889634f;
@@ -201,12 +205,14 @@ int fa_b200_fwd(const fa_b200_params* p) {
   const bool persistent = persistent_env < 0 ? auto_persistent : persistent_env == 1;
   kp.rotate = (persistent && kp.causal) ? 1 : 0;
   const cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+  const unsigned grid = static_cast<unsigned>(
+      persistent && items > st.resident_ctas ? st.resident_ctas : items);
   if (persistent) {
-    const unsigned grid = static_cast<unsigned>(items < st.resident_ctas ? items : st.resident_ctas);
-    fa::fa_fwd_kernel<true><<<grid, fa::kNumThreads, fa::kSmemBytes, stream>>>(mq, mk, mv, mo, kp);
+    if (kp.causal) fa::fa_fwd_kernel<true, true><<<grid, fa::kNumThreads, fa::kSmemBytes, stream>>>(mq, mk, mv, mo, kp);
+    else fa::fa_fwd_kernel<true, false><<<grid, fa::kNumThreads, fa::kSmemBytes, stream>>>(mq, mk, mv, mo, kp);
   } else {
-    fa::fa_fwd_kernel<false><<<static_cast<unsigned>(items), fa::kNumThreads, fa::kSmemBytes, stream>>>(
-        mq, mk, mv, mo, kp);
+    if (kp.causal) fa::fa_fwd_kernel<false, true><<<grid, fa::kNumThreads, fa::kSmemBytes, stream>>>(mq, mk, mv, mo, kp);
+    else fa::fa_fwd_kernel<false, false><<<grid, fa::kNumThreads, fa::kSmemBytes, stream>>>(mq, mk, mv, mo, kp);
   }
   return static_cast<int>(cudaGetLastError());
 }

@@ -93,10 +93,35 @@ struct __align__(1024) SharedStorage {
 constexpr int kSmemBytes = sizeof(SharedStorage) + 1024;  // + slack to align the base to 1024
 static_assert(kCtasPerSm * (kSmemBytes + 1024) <= 227 * 1024, "two CTAs must fit in one SM");
 
+// Division by a run-time constant as multiply-high + shift (the magic pair is computed on the
+// host by make_fast_div).  Exact for 0 <= n < 2^31 and 1 <= d < 2^31.  An integer division costs
+// the softmax warps over a hundred clocks, and three of them sat on the path between two work
+// items.
+struct FastDiv {
+  uint32_t mul;
+  uint32_t shift;
+  uint32_t div;
+};
+__host__ inline FastDiv make_fast_div(uint32_t d) {
+  FastDiv f;
+  f.div = d;
+  if (d == 1) { f.mul = 0; f.shift = 0; return f; }
+  uint32_t l = 0;
+  while ((1ull << l) < d) ++l;                       // l = ceil(log2 d), 1 <= l <= 31
+  const unsigned long long p = 31 + l;
+  f.mul = static_cast<uint32_t>(((1ull << p) + d - 1) / d);   // ceil(2^p / d), fits in 32 bits
+  f.shift = l - 1;                                   // total shift p - 32
+  return f;
+}
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, const FastDiv& f) {
+  return f.div == 1 ? n : (__umulhi(n, f.mul) >> f.shift);
+}
+
 struct FwdParams {
   float* lse;                 // may be null
   int B, H, N;
   int n_qtiles;               // ceil(N / 128): work items per (batch, head)
+  FastDiv div_qtiles, div_heads;   // divisions by n_qtiles and by H
   int n_items;                // B * H * n_qtiles
   int rotate;                 // causal + persistent grid: rotate the tile order per head
   int causal;
@@ -163,7 +188,9 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // items are many and short, e.g. N = 1024 causal: 4.5 K/V tiles per item on average).
 // kPersistent = false: one CTA per item, no cross-item state in the hot loop (best for long
 // sequences and for grids too small to balance statically).
-template <bool kPersistent>
+// kCausal selects the masking code at compile time (the non-causal instantiation carries none of
+// the diagonal-tile handling).
+template <bool kPersistent, bool kCausal>
 __global__ void __launch_bounds__(kNumThreads, kCtasPerSm)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
               const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
@@ -184,15 +211,23 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
   // meets every cost equally often.
   struct Item { int b, h, q_row, ns; };
   auto decode = [&](int item) {
-    const int bh = item / p.n_qtiles;
+    const int bh = static_cast<int>(fast_div(item, p.div_qtiles));
     const int slot = item - bh * p.n_qtiles;
     int qt = slot;
-    if (p.causal) qt = p.n_qtiles - 1 - (p.rotate ? (slot + bh) % p.n_qtiles : slot);
+    if (kCausal) {
+      int rs = slot;
+      if (p.rotate) {       // (slot + bh) mod n_qtiles without a second division
+        const int bh_mod = bh - static_cast<int>(fast_div(bh, p.div_qtiles)) * p.n_qtiles;
+        rs = slot + bh_mod;
+        if (rs >= p.n_qtiles) rs -= p.n_qtiles;
+      }
+      qt = p.n_qtiles - 1 - rs;
+    }
     Item w;
-    w.b = bh / p.H;
+    w.b = static_cast<int>(fast_div(bh, p.div_heads));
     w.h = bh - w.b * p.H;
     w.q_row = qt * kBlockM;
-    w.ns = p.causal ? min(nkv, qt + 1) : nkv;   // K/V tiles this query tile attends to
+    w.ns = kCausal ? min(nkv, qt + 1) : nkv;   // K/V tiles this query tile attends to
     return w;
   };
 
@@ -470,11 +505,24 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         if (lane == 0) mbar_arrive(bar_s_free);
 
         const int col0 = j * kBlockN;
-        if (p.causal) {
-          if (col0 == w.q_row) {  // the diagonal tile: column k is visible to row r iff k <= r
+        int first_masked_chunk = 4;   // 32-column chunks from here on are invisible to this warp
+        if (kCausal) {
+          if (col0 == w.q_row) {
+            // The diagonal tile: column k is visible to row r iff k <= r.  This warp owns rows
+            // 32*warp .. 32*warp+31, so 32-column chunks are decided for the whole warp: chunks
+            // below `warp` are fully visible, chunks above are fully masked (handled below without
+            // touching the scores: they are left out of the max and exponentiated with an
+            // offset of -inf), and only chunk == warp needs a per-element test -- a quarter of
+            // the compares and selects of the naive form.
+            first_masked_chunk = warp + 1;
 #pragma unroll
-            for (int k = 0; k < kBlockN; ++k)
-              if (k > r) sv[k] = kNegInf;
+            for (int ch = 0; ch < 4; ++ch) {
+              if (ch == warp) {
+#pragma unroll
+                for (int k = 0; k < 32; ++k)
+                  if (k > lane) sv[32 * ch + k] = kNegInf;
+              }
+            }
           }
         } else if (col0 + kBlockN > p.N) {  // ragged last tile: TMA zero-fill gives score 0, not -inf
           const int lim = p.N - col0;
@@ -492,6 +540,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           for (int k = 3; k + 1 < 32; k += 2)
             m = fmax3(m, __uint_as_float(sv[o + k]), __uint_as_float(sv[o + k + 1]));
           mx[ch] = fmaxf(m, __uint_as_float(sv[o + 31]));
+          if (ch >= first_masked_chunk) mx[ch] = -CUDART_INF_F;
         }
         const float m_new = fmaxf(fmax3(mx[0], mx[1], mx[2]), fmaxf(mx[3], m_ref));
 
@@ -523,11 +572,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           }
         }
 
-        const float neg_mc = -m_ref * c;
+        const float neg_mc_all = -m_ref * c;
         float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {   // 32 scores -> 16 packed registers -> one TMEM store
           uint32_t pk[16];
+          const float neg_mc = ch >= first_masked_chunk ? -CUDART_INF_F : neg_mc_all;  // exp2(-inf) = 0
 #pragma unroll
           for (int k = 0; k < 32; k += 4) {
             const int o = 32 * ch + k;
