@@ -115,13 +115,14 @@ bool stride_ok(const int64_t s[3]) {
   return true;
 }
 
-int encode_map(CUtensorMap* map, const void* base, const fa_b200_params* p, const int64_t st[3]) {
+int encode_map(CUtensorMap* map, const void* base, const fa_b200_params* p, const int64_t st[3],
+               unsigned box_rows = fa::kBlockN) {
   // dims, innermost first: d, N, H, B.  Strides (bytes) for dims 1..3: row, head, batch.
   const cuuint64_t dims[4] = {static_cast<cuuint64_t>(p->d), static_cast<cuuint64_t>(p->N),
                               static_cast<cuuint64_t>(p->H), static_cast<cuuint64_t>(p->B)};
   const cuuint64_t strides[3] = {static_cast<cuuint64_t>(st[2]) * 2, static_cast<cuuint64_t>(st[1]) * 2,
                                  static_cast<cuuint64_t>(st[0]) * 2};
-  const cuuint32_t box[4] = {fa::kHeadDim, fa::kBlockN, 1, 1};
+  const cuuint32_t box[4] = {fa::kHeadDim, box_rows, 1, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims,
                         strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -176,7 +177,7 @@ int fa_b200_fwd(const fa_b200_params* p) {
   if ((rc = encode_map(&mq, p->q, p, p->q_strides)) != 0) return rc;
   if ((rc = encode_map(&mk, p->k, p, p->k_strides)) != 0) return rc;
   if ((rc = encode_map(&mv, p->v, p, p->v_strides)) != 0) return rc;
-  if ((rc = encode_map(&mo, p->o, p, p->o_strides)) != 0) return rc;
+  if ((rc = encode_map(&mo, p->o, p, p->o_strides, 32)) != 0) return rc;   // one 32-row slab per warp
 
   fa::FwdParams kp;
   kp.lse = p->lse;
@@ -201,7 +202,7 @@ int fa_b200_fwd(const fa_b200_params* p) {
     return e == nullptr ? -1 : (e[0] == '0' ? 0 : 1);
   }();
   const int kv_tiles = (p->N + fa::kBlockN - 1) / fa::kBlockN;
-  const bool auto_persistent = items >= 8LL * st.resident_ctas && kv_tiles <= 8;
+  const bool auto_persistent = items >= 2LL * st.resident_ctas && kv_tiles <= 8;
   const bool persistent = persistent_env < 0 ? auto_persistent : persistent_env == 1;
   kp.rotate = (persistent && kp.causal) ? 1 : 0;
   const cudaStream_t stream = static_cast<cudaStream_t>(p->stream);

@@ -68,8 +68,7 @@ constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
 constexpr uint32_t kWatchdogBase = 0x10000u;
 enum WaitId : uint32_t {
   kWaitQFull = 1, kWaitKVFull = 2, kWaitKVEmpty = 3, kWaitSFull = 4, kWaitPFull = 5,
-  kWaitOFull = 6, kWaitDrain = 7, kWaitSFree = 8, kWaitQEmpty = 9, kWaitOFree = 10,
-  kWaitOStaged = 11, kWaitStageFree = 12
+  kWaitOFull = 6, kWaitDrain = 7, kWaitSFree = 8, kWaitQEmpty = 9, kWaitOFree = 10
 };
 
 struct __align__(1024) SharedStorage {
@@ -85,8 +84,6 @@ struct __align__(1024) SharedStorage {
   uint64_t p_full;               // P written to TMEM by all four softmax warps
   uint64_t o_full;               // O += P V_j finished (P reusable, O stable)
   uint64_t o_free;               // the epilogue has read O: the next item may overwrite it
-  uint64_t o_staged;             // all four softmax warps have written their rows to o_stage
-  uint64_t stage_free;           // the previous TMA store has finished reading o_stage
   uint32_t tmem_base;
   uint32_t abort;
 };
@@ -240,8 +237,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     mbar_init(smem_u32(&sm.p_full), kNumSoftmaxWarps);
     mbar_init(smem_u32(&sm.o_full), 1);
     mbar_init(smem_u32(&sm.o_free), kNumSoftmaxWarps);
-    mbar_init(smem_u32(&sm.o_staged), kNumSoftmaxWarps);
-    mbar_init(smem_u32(&sm.stage_free), 1);
     for (int i = 0; i < kKVSlots; ++i) {
       mbar_init(smem_u32(&sm.kv_full[i]), 1);
       mbar_init(smem_u32(&sm.kv_empty[i]), 1);
@@ -412,8 +407,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     const uint32_t bar_p = smem_u32(&sm.p_full);
     const uint32_t bar_o = smem_u32(&sm.o_full);
     const uint32_t bar_o_free = smem_u32(&sm.o_free);
-    const uint32_t bar_o_staged = smem_u32(&sm.o_staged);
-    const uint32_t bar_stage_free = smem_u32(&sm.stage_free);
     // this thread's row of the staging tile; 16-byte chunk c goes to position c ^ (r & 7)
     // (the 128-byte swizzle the TMA store expects)
     const uint32_t stage_row = smem_u32(sm.o_stage) + r * 128;
@@ -439,15 +432,11 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_o_free);
-      // The staging tile is free once the previous item's TMA store has read it.  The thread
-      // that issued that store waits for it and tells the others.
-      if (owed_n > 0) {
-        if (threadIdx.x == 0) {
-          tma_store_wait_read<0>();
-          mbar_arrive(bar_stage_free);
-        }
-        if (!wait_bar_warp(bar_stage_free, (owed_n - 1) & 1, watch, kWaitStageFree)) return false;
-      }
+      // Each warp stages and stores its own 32 rows, so no other warp is involved: lane 0 issued
+      // the previous store from this slab and makes sure it has been read before the slab is
+      // rewritten (it was issued a whole work item ago).
+      if (lane == 0) tma_store_wait_read<0>();
+      __syncwarp();
       const float inv_l = 1.0f / owed_l;
 #pragma unroll
       for (int ck = 0; ck < 8; ++ck) {
@@ -460,15 +449,10 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       }
       fence_proxy_async_smem();     // generic-proxy writes -> visible to the TMA engine
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_o_staged);
-      bool good = true;
-      if (warp == 0) {
-        good = wait_bar_warp(bar_o_staged, owed_n & 1, watch, kWaitOStaged);
-        if (good && lane == 0) {    // rows >= N are clipped by the tensor map
-          tma_store_4d(&tmap_o, smem_u32(sm.o_stage), 0, owed_q_row, owed_h, owed_b);
-          tma_store_commit();
-        }
-        __syncwarp();
+      const int slab_row = owed_q_row + 32 * warp;
+      if (lane == 0 && slab_row < p.N) {   // rows >= N inside the slab are clipped by the tensor map
+        tma_store_4d(&tmap_o, smem_u32(sm.o_stage) + warp * (32 * 128), 0, slab_row, owed_h, owed_b);
+        tma_store_commit();
       }
       const int row = owed_q_row + r;
       if (p.lse != nullptr && row < p.N) {
@@ -477,7 +461,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             0.6931471805599453f * (owed_m * c + log2f(owed_l));
       }
       owed = false;
-      return good;
+      return true;
     };
 
     const int item_stride = kPersistent ? static_cast<int>(gridDim.x) : p.n_items;
@@ -615,8 +599,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       ok = wait_bar_warp(bar_o, (g - 1) & 1, watch, kWaitOFull);
       if (ok) ok = epilogue();
     }
-    // the last TMA store must have read the staging tile before shared memory goes away
-    if (threadIdx.x == 0) tma_store_wait_read<0>();
+    // each warp's last TMA store must have read its slab before shared memory goes away
+    if (lane == 0) tma_store_wait_read<0>();
   }
 
   // ---- teardown: every TMEM access above is complete (loads waited, MMAs observed via o_full)
