@@ -120,7 +120,9 @@ struct FwdParams {
   int n_qtiles;               // ceil(N / 128): work items per (batch, head)
   FastDiv div_qtiles, div_heads;   // divisions by n_qtiles and by H
   int n_items;                // B * H * n_qtiles
-  int rotate;                 // causal + persistent grid: rotate the tile order per head
+  int paired;                 // persistent causal schedule with an even tile count: complementary pairs
+  int n_units;                // B * H * n_qtiles / 2 when paired
+  FastDiv div_half;           // division by n_qtiles / 2
   int causal;
   float scale_log2;           // softmax_scale * log2(e)
   unsigned int* status;       // [4] watchdog words in global memory
@@ -201,31 +203,47 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
   const int lane = threadIdx.x & 31;
   const int nkv = (p.N + kBlockN - 1) / kBlockN;
 
-  // Work item -> (batch, head, query tile).  A head's tiles are adjacent in the list, so CTAs
-  // that run side by side share that head's K/V in L2.  In causal mode tile t costs t+1 K/V tiles
-  // and the heaviest tile of a head comes first; with a persistent grid the order inside a head
-  // is instead rotated by the head index, so that a CTA striding through the list by gridDim.x
-  // meets every cost equally often.
+  // The n-th work item of this CTA -> (batch, head, query tile); false when the CTA is done.
+  // A head's tiles are adjacent in the list, so CTAs that run side by side share that head's K/V
+  // in L2.  In causal mode tile t costs t+1 K/V tiles.  Three schedules:
+  //   one CTA per item      heaviest tile of a head first, the hardware balances dynamically;
+  //   persistent, paired    (even tile count) the CTA takes tile nq-1-s and then its complement
+  //                         s of the same head: every pair costs nq+1 K/V tiles, so a CTA striding
+  //                         through the pairs by gridDim.x gets equal work;
+  //   persistent, rotated   (odd tile count, or non-causal) stride through single items, the tile
+  //                         order inside a head rotated by the head index.
   struct Item { int b, h, q_row, ns; };
-  auto decode = [&](int item) {
-    const int bh = static_cast<int>(fast_div(item, p.div_qtiles));
-    const int slot = item - bh * p.n_qtiles;
-    int qt = slot;
-    if (kCausal) {
-      int rs = slot;
-      if (p.rotate) {       // (slot + bh) mod n_qtiles without a second division
-        const int bh_mod = bh - static_cast<int>(fast_div(bh, p.div_qtiles)) * p.n_qtiles;
-        rs = slot + bh_mod;
-        if (rs >= p.n_qtiles) rs -= p.n_qtiles;
+  auto get_item = [&](int n, Item& w) -> bool {
+    int bh, qt;
+    if (kPersistent && kCausal && p.paired) {
+      const int unit = blockIdx.x + (n >> 1) * gridDim.x;
+      if (unit >= p.n_units) return false;
+      const int half_q = p.n_qtiles >> 1;
+      bh = static_cast<int>(fast_div(unit, p.div_half));
+      const int sidx = unit - bh * half_q;
+      qt = (n & 1) ? sidx : p.n_qtiles - 1 - sidx;
+    } else {
+      if (!kPersistent && n > 0) return false;
+      const int item = blockIdx.x + n * gridDim.x;
+      if (item >= p.n_items) return false;
+      bh = static_cast<int>(fast_div(item, p.div_qtiles));
+      const int slot = item - bh * p.n_qtiles;
+      qt = slot;
+      if (kCausal) {
+        int rs = slot;
+        if (kPersistent) {       // (slot + bh) mod n_qtiles without a second division
+          const int bh_mod = bh - static_cast<int>(fast_div(bh, p.div_qtiles)) * p.n_qtiles;
+          rs = slot + bh_mod;
+          if (rs >= p.n_qtiles) rs -= p.n_qtiles;
+        }
+        qt = p.n_qtiles - 1 - rs;
       }
-      qt = p.n_qtiles - 1 - rs;
     }
-    Item w;
     w.b = static_cast<int>(fast_div(bh, p.div_heads));
     w.h = bh - w.b * p.H;
     w.q_row = qt * kBlockM;
     w.ns = kCausal ? min(nkv, qt + 1) : nkv;   // K/V tiles this query tile attends to
-    return w;
+    return true;
   };
 
   // ---- one-time setup
@@ -286,9 +304,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           ++it;
         }
       };
-      const int item_stride = kPersistent ? static_cast<int>(gridDim.x) : p.n_items;
-      for (int item = blockIdx.x; item < p.n_items && ok; item += item_stride, ++n) {
-        const Item w = decode(item);
+      for (; ok; ++n) {
+        Item w;
+        if (!get_item(n, w)) break;
         if (n > 0) ok = wait_bar_warp(smem_u32(&sm.q_empty), (n - 1) & 1, watch, kWaitQEmpty);
         if (!ok) break;
         if (elect_one()) {
@@ -350,9 +368,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       // tile whose PV comes next, `n` = local item index.
       bool ok = true;
       int it = 1, g = 0, n = 0;
-      int item = blockIdx.x;
-      Item w = decode(item < p.n_items ? item : 0);
-      if (item < p.n_items) {
+      Item w;
+      bool have_item = get_item(0, w);
+      if (have_item) {
         ok = wait_bar_warp(smem_u32(&sm.q_full), 0, watch, kWaitQFull) &&
              wait_bar_warp(smem_u32(&sm.kv_full[0]), 0, watch, kWaitKVFull);
         if (ok) {
@@ -360,11 +378,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           issue_s(0, w.ns == 1);
         }
       }
-      const int item_stride = kPersistent ? static_cast<int>(gridDim.x) : p.n_items;
-      for (; item < p.n_items && ok; item += item_stride, ++n) {
-        const int next_item = item + item_stride;
-        const bool has_next_item = kPersistent && next_item < p.n_items;
-        const Item wn = decode(has_next_item ? next_item : item);
+      for (; have_item && ok; ++n) {
+        Item wn = w;
+        const bool has_next_item = get_item(n + 1, wn);
         for (int j = 0; j < w.ns && ok; ++j, ++g) {
           const int itv = it;          // V_j of this item
           const int itk = it + 1;      // the next K in ring order: K_{j+1}, or K_0 of the next item
@@ -391,6 +407,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           it += 2;
         }
         w = wn;
+        have_item = has_next_item;
       }
     }
   } else {
@@ -464,9 +481,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       return true;
     };
 
-    const int item_stride = kPersistent ? static_cast<int>(gridDim.x) : p.n_items;
-    for (int item = blockIdx.x; item < p.n_items && ok; item += item_stride, ++n) {
-      const Item w = decode(item);
+    for (; ok; ++n) {
+      Item w;
+      if (!get_item(n, w)) break;
       float m_ref = -CUDART_INF_F;  // max the exponentials are currently taken against (raw scores)
       float l = 0.f;                // running sum of exp2((s - m_ref) * c)
 
