@@ -93,7 +93,9 @@ def gpt_tiny(mi):
 
 
 if __name__ == "__main__":
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference")
+    ref_root = sys.argv[1]
     here = __file__.rsplit("/", 1)[0]
     mi = import_reference(ref_root)
     np.savez_compressed(f"{here}/attn_manual_cases.npz", **attention_cases(mi))

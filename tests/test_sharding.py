@@ -23,7 +23,7 @@ def test_shard_heads_partitions_exactly(total, world):
     assert sizes == sorted(sizes, reverse=True)               # the extra heads go to the first ranks
 
 
-def test_config5_split_matches_design_note():
+def test_hundred_heads_over_eight_ranks():
     sizes = [workloads.shard_heads(100, 8, r) for r in range(8)]
     assert [s.stop - s.start for s in sizes] == [13, 13, 13, 13, 12, 12, 12, 12]
 
