@@ -378,6 +378,40 @@ def main():
         if cfa.last_status() != 0:
             raise SystemExit("kernel watchdog fired during the prefill runs")
 
+    # ---------------------------------------------------------------- decode step (KV-cache attention)
+    decode = []
+    if not args.no_sweep:
+        for (db, dh, dn) in ((32, 25, 1024), (1, 25, 1024), (8, 25, 8192)):
+            g = torch.Generator(device="cuda").manual_seed(11 + rank)
+            dq = torch.randn(db, dh, 64, device="cuda", generator=g).bfloat16()
+            # several cache sets rotated between launches so that K/V come from HBM, not from L2
+            n_sets = max(1, min(8, int(400e6 // (2 * db * dh * dn * 128)) + 1))
+            caches = [(torch.randn(db, dh, dn, 64, device="cuda", generator=g).bfloat16(),
+                       torch.randn(db, dh, dn, 64, device="cuda", generator=g).bfloat16())
+                      for _ in range(n_sets)]
+            do = torch.empty_like(dq)
+            for i in range(5):
+                cfa.decode(dq, *caches[i % n_sets], dn, out=do)
+            barrier(world)
+            steps = 40
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(steps):
+                cfa.decode(dq, *caches[i % n_sets], dn, out=do)
+            e1.record()
+            barrier(world)
+            dms = max_over_ranks(e0.elapsed_time(e1) / steps, world)
+            nbytes = 2.0 * db * dh * dn * 128                      # K and V read once
+            decode.append({"B_per_gpu": db, "H": dh, "kv_len": dn, "us_per_step": round(dms * 1e3, 2),
+                           "gbs_per_gpu": round(nbytes / (dms * 1e-3) / 1e9, 1),
+                           "frac_of_hbm_peak": round(nbytes / (dms * 1e-3) / 1e9 / peaks["hbm_gbs"], 3),
+                           "cache_sets_rotated": n_sets,
+                           "kernels": "fa::fa_decode_partial_kernel (+ fa::fa_decode_combine_kernel when keys are split)"})
+            del caches, dq, do
+            torch.cuda.empty_cache()
+        if cfa.last_status() != 0:
+            raise SystemExit("kernel watchdog fired during the decode runs")
+
     # ---------------------------------------------------------------- CPU baseline (rank 0, N=1 only)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -410,7 +444,7 @@ def main():
             "gpu_launches": args.steps,
             "clocks": clocks,
             "cpu_baseline": cpu,
-            "extra": {"sweep": sweep, "gpt2_prefill": prefill},
+            "extra": {"sweep": sweep, "gpt2_prefill": prefill, "decode_step": decode},
         }
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -50,6 +50,7 @@ extern "C" {
 #define FA_B200_ERR_TENSORMAP     -9  /* the driver refused a TMA descriptor               */
 #define FA_B200_ERR_DRIVER       -10  /* cuTensorMapEncodeTiled could not be resolved      */
 #define FA_B200_ERR_BUILD        -11  /* kernel image / launch configuration mismatch         */
+#define FA_B200_ERR_WORKSPACE    -12  /* decode workspace NULL, too small or misaligned    */
 
 typedef struct fa_b200_params {
   const void* q;            /* bf16 [B,H,N,d] */
@@ -95,6 +96,48 @@ int fa_b200_device_ok(int device);
  * The reference has no counterpart (its cudaGetLastError result is dropped,
  * src/cpp/torch_bind.cpp:34-39). */
 int fa_b200_last_status(int device, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Single-query ("decode") attention against a K/V cache: one new token per sequence.
+ *
+ *   o[b,h,:] = softmax_j(scale * q[b,h,:] . k[b,h,j,:]) v[b,h,j,:],   0 <= j < kv_len
+ *
+ * The reference has no such entry point: its generate() re-runs the whole prefix through the
+ * prefill kernel for every new token (src/py/model_inference.py:199-228).  This is the attention
+ * step of the same loop with a KV cache.
+ *
+ * q and o are bf16 [B, H, 64] (strides {batch, head} in elements, multiples of 8); the caches are
+ * bf16 [B, H, >= kv_len, 64] with strides {batch, head, row}; lse (optional) is fp32 [B, H].
+ * With few (batch, head) pairs the keys of a head are processed in several chunks whose partial
+ * results pass through `workspace`: device memory of at least
+ * fa_b200_decode_workspace_bytes(B, H, kv_len) bytes, 16-byte aligned, owned by the caller and not
+ * shared by calls that may overlap on the GPU (it may be NULL when that function returns 0).
+ */
+typedef struct fa_b200_decode_params {
+  const void* q;
+  const void* k_cache;
+  const void* v_cache;
+  void*       o;
+  float*      lse;            /* may be NULL */
+  void*       workspace;      /* see above */
+  int64_t     workspace_bytes;
+  int32_t     B, H, kv_len, d;   /* d must be 64, kv_len >= 1 */
+  int64_t     q_strides[2];   /* elements: {batch, head} */
+  int64_t     o_strides[2];
+  int64_t     k_strides[3];   /* elements: {batch, head, row} */
+  int64_t     v_strides[3];
+  float       softmax_scale;  /* 0 selects 1/sqrt(d) */
+  int32_t     device;
+  void*       stream;
+} fa_b200_decode_params;
+
+/* Bytes of workspace fa_b200_decode needs for this problem size (0 when the keys of a head are
+ * not split).  Negative on bad arguments.  No CUDA call is made. */
+int64_t fa_b200_decode_workspace_bytes(int32_t B, int32_t H, int32_t kv_len);
+
+/* Enqueue one decode-attention step on p->stream.  Return values as fa_b200_fwd;
+ * FA_B200_ERR_WORKSPACE when the workspace is missing, too small or misaligned. */
+int fa_b200_decode(const fa_b200_decode_params* p);
 
 /* FA_B200_ABI_VERSION the library was built with. */
 int fa_b200_abi_version(void);

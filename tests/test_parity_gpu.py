@@ -266,6 +266,52 @@ def test_forward_host_pipeline_matches_device_call(cfa):
     assert torch.equal(out, cfa.forward(q.cuda(), k.cuda(), v.cuda(), causal=False).cpu())
 
 
+def _decode_oracle(q, k, v, kv_len, scale=None):
+    """One query row against the first kv_len cache rows, with the prefill oracle (no mask)."""
+    orc = _oracle()
+    return orc.manual_attention(q.float().cpu().unsqueeze(2), k[:, :, :kv_len].float().cpu(),
+                                v[:, :, :kv_len].float().cpu(), causal=False, softmax_scale=scale,
+                                return_lse=True)
+
+
+@pytest.mark.parametrize("B,H,kv_len", [(1, 1, 1), (1, 2, 7), (2, 3, 64), (1, 25, 1000), (3, 5, 129),
+                                        (32, 25, 1024), (1, 12, 4096), (2, 1, 33)])
+def test_decode_parity(cfa, B, H, kv_len):
+    """Single-query attention over a KV cache (split over chunks or not) against the oracle."""
+    torch.manual_seed(B * 1000 + H * 10 + kv_len)
+    cache_len = kv_len + 37                       # rows past kv_len must be ignored
+    q = torch.randn(B, H, 64).bfloat16().cuda()
+    k = torch.randn(B, H, cache_len, 64).bfloat16().cuda()
+    v = torch.randn(B, H, cache_len, 64).bfloat16().cuda()
+    k[:, :, kv_len:] = 1e4                        # poison: would dominate if read
+    o, lse = cfa.decode(q, k, v, kv_len, return_lse=True)
+    assert cfa.last_status() == 0
+    assert o.shape == (B, H, 64) and lse.shape == (B, H)
+    ro, rl = _decode_oracle(q, k, v, kv_len)
+    d = (o.float().cpu() - ro[:, :, 0]).abs()
+    assert d.max().item() <= MAX_ABS and d.mean().item() <= MEAN_ABS
+    assert ((lse.cpu() - rl[:, :, 0]).abs() <= 1e-3 * rl[:, :, 0].abs().clamp_min(1.0)).all()
+
+
+def test_decode_matches_last_row_of_prefill_and_strided_cache(cfa):
+    """The new token's decode step equals the last row of the causal prefill over the same keys;
+    caches laid out [B, N, H, d] (as a generation loop would append them) are read in place."""
+    torch.manual_seed(5)
+    B, H, N = 2, 4, 300
+    q, k, v = (torch.randn(B, N, H, 64).bfloat16().cuda().transpose(1, 2) for _ in range(3))
+    full = cfa.forward(q, k, v)                                   # causal prefill, strided views
+    step = cfa.decode(q[:, :, N - 1:N, :], k, v, N)               # [B, H, 1, 64] query view
+    assert step.shape == (B, H, 1, 64)
+    assert torch.allclose(step[:, :, 0].float(), full[:, :, N - 1].float(), rtol=1e-2, atol=1e-2)
+    out = torch.empty(B, H, 64, dtype=torch.bfloat16, device="cuda")
+    r = cfa.decode(q[:, :, 10], k, v, 11, softmax_scale=0.3, out=out)
+    assert r.data_ptr() == out.data_ptr()
+    ro, _ = _decode_oracle(q[:, :, 10], k, v, 11, scale=0.3)
+    assert (out.float().cpu() - ro[:, :, 0]).abs().max().item() <= MAX_ABS
+    with pytest.raises(RuntimeError, match="kv_len"):
+        cfa.decode(q[:, :, 0], k, v, N + 1)
+
+
 def test_non_default_stream(cfa):
     torch.manual_seed(31)
     q, k, v = (torch.randn(1, 2, 512, 64, device="cuda", dtype=torch.bfloat16) for _ in range(3))

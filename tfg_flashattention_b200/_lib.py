@@ -26,8 +26,21 @@ class FaParams(ctypes.Structure):
     ]
 
 
+class FaDecodeParams(ctypes.Structure):
+    """struct fa_b200_decode_params (include/fa_b200.h)."""
+    _fields_ = [
+        ("q", ctypes.c_void_p), ("k_cache", ctypes.c_void_p), ("v_cache", ctypes.c_void_p),
+        ("o", ctypes.c_void_p), ("lse", ctypes.c_void_p),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_int64),
+        ("B", ctypes.c_int32), ("H", ctypes.c_int32), ("kv_len", ctypes.c_int32), ("d", ctypes.c_int32),
+        ("q_strides", ctypes.c_int64 * 2), ("o_strides", ctypes.c_int64 * 2),
+        ("k_strides", ctypes.c_int64 * 3), ("v_strides", ctypes.c_int64 * 3),
+        ("softmax_scale", ctypes.c_float), ("device", ctypes.c_int32), ("stream", ctypes.c_void_p),
+    ]
+
+
 EXPORTS = ("fa_b200_fwd", "fa_b200_validate", "fa_b200_strerror", "fa_b200_device_ok",
-           "fa_b200_last_status", "fa_b200_abi_version")
+           "fa_b200_last_status", "fa_b200_abi_version", "fa_b200_decode", "fa_b200_decode_workspace_bytes")
 
 _lib = None
 
@@ -53,6 +66,10 @@ def load() -> ctypes.CDLL:
     lib.fa_b200_device_ok.restype = ctypes.c_int
     lib.fa_b200_last_status.argtypes = [ctypes.c_int, ctypes.c_void_p]
     lib.fa_b200_last_status.restype = ctypes.c_int
+    lib.fa_b200_decode.argtypes = [ctypes.POINTER(FaDecodeParams)]
+    lib.fa_b200_decode.restype = ctypes.c_int
+    lib.fa_b200_decode_workspace_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
+    lib.fa_b200_decode_workspace_bytes.restype = ctypes.c_int64
     lib.fa_b200_abi_version.argtypes = []
     lib.fa_b200_abi_version.restype = ctypes.c_int
     if lib.fa_b200_abi_version() != ABI_VERSION:

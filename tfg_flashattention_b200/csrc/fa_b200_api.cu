@@ -11,6 +11,7 @@
 #include <mutex>
 
 #include "../../include/fa_b200.h"
+#include "fa_decode_sm100.cuh"
 #include "fa_fwd_sm100.cuh"
 
 namespace {
@@ -227,6 +228,109 @@ int fa_b200_fwd(const fa_b200_params* p) {
   return static_cast<int>(cudaGetLastError());
 }
 
+// ------------------------------------------------------------------------------------ decode
+namespace {
+
+constexpr int kDecodeTargetCtas = 592;   // 4 CTAs per SM on a 148-SM part: enough loads in flight
+
+// How the keys of one head are cut: `splits` chunks of `rows` rows (a multiple of the 16 lane
+// groups of a CTA).  The same rule sizes the workspace and launches the kernel.
+void decode_split(int B, int H, int kv_len, int* splits, int* rows) {
+  const long long heads = static_cast<long long>(B) * H;
+  long long want = (kDecodeTargetCtas + heads - 1) / heads;
+  const long long max_splits = (kv_len + 63) / 64;            // at least 64 rows per chunk
+  if (want > max_splits) want = max_splits;
+  if (want < 1) want = 1;
+  long long r = (kv_len + want - 1) / want;
+  r = (r + fa::kDecodeGroups - 1) / fa::kDecodeGroups * fa::kDecodeGroups;
+  *rows = static_cast<int>(r);
+  *splits = static_cast<int>((kv_len + r - 1) / r);
+}
+
+bool stride_ok_n(const int64_t* s, int n) {
+  for (int i = 0; i < n; ++i)
+    if (s[i] <= 0 || (s[i] % 8) != 0) return false;
+  return true;
+}
+
+int decode_validate(const fa_b200_decode_params* p) {
+  if (p == nullptr || p->q == nullptr || p->k_cache == nullptr || p->v_cache == nullptr ||
+      p->o == nullptr)
+    return FA_B200_ERR_NULL;
+  if (p->d != fa::kHeadDim) return FA_B200_ERR_HEAD_DIM;
+  if (p->B < 0 || p->H < 0 || p->kv_len < 1) return FA_B200_ERR_SHAPE;
+  if (static_cast<long long>(p->B) * p->H > 0x7fffffffLL / 64) return FA_B200_ERR_SHAPE;
+  if (!stride_ok_n(p->q_strides, 2) || !stride_ok_n(p->o_strides, 2) || !stride_ok_n(p->k_strides, 3) ||
+      !stride_ok_n(p->v_strides, 3))
+    return FA_B200_ERR_STRIDE;
+  const uintptr_t ptrs[4] = {reinterpret_cast<uintptr_t>(p->q), reinterpret_cast<uintptr_t>(p->k_cache),
+                             reinterpret_cast<uintptr_t>(p->v_cache), reinterpret_cast<uintptr_t>(p->o)};
+  for (uintptr_t a : ptrs)
+    if (a & 15u) return FA_B200_ERR_ALIGN;
+  if (p->lse != nullptr && (reinterpret_cast<uintptr_t>(p->lse) & 3u)) return FA_B200_ERR_ALIGN;
+  if (!(p->softmax_scale >= 0.0f) || std::isinf(p->softmax_scale)) return FA_B200_ERR_SCALE;
+  if (p->device < 0 || p->device >= kMaxDevices) return FA_B200_ERR_DEVICE;
+  return FA_B200_OK;
+}
+
+}  // namespace
+
+int64_t fa_b200_decode_workspace_bytes(int32_t B, int32_t H, int32_t kv_len) {
+  if (B < 0 || H < 0 || kv_len < 1) return FA_B200_ERR_SHAPE;
+  if (B == 0 || H == 0) return 0;
+  int splits = 1, rows = 0;
+  decode_split(B, H, kv_len, &splits, &rows);
+  if (splits == 1) return 0;
+  return static_cast<int64_t>(B) * H * splits * fa::kDecodePartial * static_cast<int64_t>(sizeof(float));
+}
+
+int fa_b200_decode(const fa_b200_decode_params* p) {
+  int rc = decode_validate(p);
+  if (rc != FA_B200_OK) return rc;
+  if (p->B == 0 || p->H == 0) return FA_B200_OK;
+  int splits = 1, rows = 0;
+  decode_split(p->B, p->H, p->kv_len, &splits, &rows);
+  if (splits > 1) {
+    const int64_t need = fa_b200_decode_workspace_bytes(p->B, p->H, p->kv_len);
+    if (p->workspace == nullptr || p->workspace_bytes < need ||
+        (reinterpret_cast<uintptr_t>(p->workspace) & 15u))
+      return FA_B200_ERR_WORKSPACE;
+  }
+  DeviceGuard guard(p->device);
+  if (guard.error) return guard.error;
+  DeviceState& st = g_dev[p->device];
+  std::call_once(st.once, init_device, p->device);
+  if (st.init_error) return st.init_error;
+
+  fa::DecodeParams kp;
+  kp.q = static_cast<const __nv_bfloat16*>(p->q);
+  kp.k = static_cast<const __nv_bfloat16*>(p->k_cache);
+  kp.v = static_cast<const __nv_bfloat16*>(p->v_cache);
+  kp.o = static_cast<__nv_bfloat16*>(p->o);
+  kp.lse = p->lse;
+  kp.scratch = static_cast<float*>(p->workspace);
+  kp.q_sb = p->q_strides[0]; kp.q_sh = p->q_strides[1];
+  kp.o_sb = p->o_strides[0]; kp.o_sh = p->o_strides[1];
+  kp.k_sb = p->k_strides[0]; kp.k_sh = p->k_strides[1]; kp.k_sn = p->k_strides[2];
+  kp.v_sb = p->v_strides[0]; kp.v_sh = p->v_strides[1]; kp.v_sn = p->v_strides[2];
+  kp.B = p->B; kp.H = p->H; kp.kv_len = p->kv_len;
+  kp.splits = splits;
+  kp.rows_per_split = rows;
+  const float scale = p->softmax_scale > 0.0f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(p->d));
+  kp.scale_log2 = scale * 1.4426950408889634f;
+
+  const cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+  const dim3 grid(static_cast<unsigned>(p->B * p->H), static_cast<unsigned>(splits));
+  fa::fa_decode_partial_kernel<<<grid, fa::kDecodeThreads, 0, stream>>>(kp);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (splits > 1) {
+    fa::fa_decode_combine_kernel<<<static_cast<unsigned>(p->B * p->H), 64, 0, stream>>>(kp);
+    e = cudaGetLastError();
+  }
+  return static_cast<int>(e);
+}
+
 int fa_b200_device_ok(int device) {
   if (device < 0) return FA_B200_ERR_DEVICE;
   int count = 0;
@@ -285,6 +389,7 @@ const char* fa_b200_strerror(int code) {
     case FA_B200_ERR_ARCH: return "fa_b200: device is not compute capability 10.x (B200); there is no fallback";
     case FA_B200_ERR_TENSORMAP: return "fa_b200: the driver rejected a TMA tensor map (check strides and sizes)";
     case FA_B200_ERR_DRIVER: return "fa_b200: cuTensorMapEncodeTiled is not available from this driver";
+    case FA_B200_ERR_WORKSPACE: return "fa_b200: decode workspace is NULL, too small or not 16-byte aligned";
     case FA_B200_ERR_BUILD: return "fa_b200: the kernel image does not match this library's launch configuration; rebuild it";
     default: break;
   }

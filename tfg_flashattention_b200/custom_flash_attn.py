@@ -29,7 +29,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["forward", "forward_host", "last_status"]
+__all__ = ["forward", "forward_host", "decode", "last_status"]
 
 
 def _check_input(t: torch.Tensor, name: str) -> None:
@@ -101,6 +101,99 @@ def forward(Q, K, V, causal=True, return_lse=False, softmax_scale=None, out=None
     if rc != 0:
         raise RuntimeError(f"custom_flash_attn.forward failed ({rc}): {_lib.strerror(rc)}")
     return (O, lse) if return_lse else O
+
+
+_decode_workspaces = {}
+
+
+def decode(Q, K_cache, V_cache, kv_len, return_lse=False, softmax_scale=None, out=None):
+    """Single-query attention against a K/V cache (one generation step; the reference has no
+    counterpart -- its generate() recomputes the whole prefix, model_inference.py:199-228).
+
+    Q [B, H, 64] (or [B, H, 1, 64]) bf16; K_cache, V_cache [B, H, >= kv_len, 64] bf16 (any row /
+    head / batch strides that are multiples of 8 elements); attends rows 0 .. kv_len-1.
+    Returns O shaped like Q (and LSE [B, H] fp32 when asked).  The split-KV workspace is a cached
+    torch buffer per device; calls on one stream may share it, calls that overlap on different
+    streams of one device must not (pass through separate processes or serialise them)."""
+    squeeze = Q.dim() == 4
+    q3 = Q[:, :, 0, :] if squeeze else Q
+    for t, name in ((q3, "Q"), (K_cache, "K_cache"), (V_cache, "V_cache")):
+        if not t.is_cuda:
+            raise RuntimeError(f"{name} must be a CUDA tensor")
+        if t.dtype != torch.bfloat16:
+            raise RuntimeError("Unsupported tensor dtype. Use bfloat16.")
+    if squeeze and Q.shape[2] != 1:
+        raise RuntimeError("Q must hold one query row per head: [B, H, 64] or [B, H, 1, 64]")
+    if q3.dim() != 3 or K_cache.dim() != 4 or V_cache.dim() != 4:
+        raise RuntimeError("expected Q [B, H, d] and caches [B, H, N, d]")
+    B, H, d = q3.shape
+    if K_cache.shape[:2] != (B, H) or V_cache.shape != K_cache.shape or K_cache.shape[3] != d:
+        raise RuntimeError("Q, K_cache and V_cache disagree on B, H or d")
+    kv_len = int(kv_len)
+    if not 1 <= kv_len <= K_cache.shape[2]:
+        raise RuntimeError("kv_len must be between 1 and the cache length")
+    for t, name in ((q3, "Q"), (K_cache, "K_cache"), (V_cache, "V_cache")):
+        if t.stride(-1) != 1:
+            raise RuntimeError(f"{name}: the last dimension must be dense (stride 1)")
+    if out is None:
+        O = torch.empty((B, H, d), dtype=torch.bfloat16, device=Q.device)
+    else:
+        O = out[:, :, 0, :] if out.dim() == 4 else out
+        if O.shape != (B, H, d) or O.dtype != torch.bfloat16 or O.device != Q.device or O.stride(-1) != 1:
+            raise RuntimeError("out must match Q in shape, dtype and device")
+    lse = torch.empty((B, H), dtype=torch.float32, device=Q.device) if return_lse else None
+
+    lib = _lib.load()
+    need = lib.fa_b200_decode_workspace_bytes(B, H, kv_len)
+    if need < 0:
+        raise RuntimeError(f"custom_flash_attn.decode failed ({need}): {_lib.strerror(int(need))}")
+    ws = None
+    if need > 0:
+        ws = _decode_workspaces.get(Q.device)
+        if ws is None or ws.numel() < need:
+            ws = _decode_workspaces[Q.device] = torch.empty(max(need, 1 << 20), dtype=torch.uint8,
+                                                            device=Q.device)
+
+    def two(t):      # {batch, head} strides; size-1 dimensions get a canonical stride
+        sb, sh = t.stride(0), t.stride(1)
+        if H == 1:
+            sh = 64
+        if B == 1:
+            sb = max(H * sh, 64)
+        return (ctypes.c_int64 * 2)(sb, sh)
+
+    def three(t):
+        sb, sh, sn = t.stride(0), t.stride(1), t.stride(2)
+        if t.shape[2] == 1:
+            sn = 64
+        if H == 1:
+            sh = max(t.shape[2] * sn, 64)
+        if B == 1:
+            sb = max(H * sh, 64)
+        return (ctypes.c_int64 * 3)(sb, sh, sn)
+
+    p = _lib.FaDecodeParams()
+    p.q, p.k_cache, p.v_cache, p.o = q3.data_ptr(), K_cache.data_ptr(), V_cache.data_ptr(), O.data_ptr()
+    p.lse = lse.data_ptr() if lse is not None else None
+    p.workspace = ws.data_ptr() if ws is not None else None
+    p.workspace_bytes = ws.numel() if ws is not None else 0
+    p.B, p.H, p.kv_len, p.d = B, H, kv_len, d
+    if B * H > 0:
+        p.q_strides, p.o_strides = two(q3), two(O)
+        p.k_strides, p.v_strides = three(K_cache), three(V_cache)
+    else:
+        p.q_strides = p.o_strides = (ctypes.c_int64 * 2)(64, 64)
+        p.k_strides = p.v_strides = (ctypes.c_int64 * 3)(64, 64, 64)
+        for name in ("q", "k_cache", "v_cache", "o"):
+            setattr(p, name, getattr(p, name) or 16)
+    p.softmax_scale = 0.0 if softmax_scale is None else float(softmax_scale)
+    p.device = Q.device.index if Q.device.index is not None else torch.cuda.current_device()
+    p.stream = torch.cuda.current_stream(Q.device).cuda_stream
+    rc = lib.fa_b200_decode(ctypes.byref(p))
+    if rc != 0:
+        raise RuntimeError(f"custom_flash_attn.decode failed ({rc}): {_lib.strerror(rc)}")
+    result = out if out is not None else (O.unsqueeze(2) if squeeze else O)
+    return (result, lse) if return_lse else result
 
 
 class _HostPipeline:
