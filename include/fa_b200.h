@@ -51,6 +51,7 @@ extern "C" {
 #define FA_B200_ERR_DRIVER       -10  /* cuTensorMapEncodeTiled could not be resolved      */
 #define FA_B200_ERR_BUILD        -11  /* kernel image / launch configuration mismatch         */
 #define FA_B200_ERR_WORKSPACE    -12  /* decode workspace NULL, too small or misaligned    */
+#define FA_B200_ERR_STATIC_SCRATCH -13 /* problem needs more than FA_B200_STATIC_SCRATCH_BYTES */
 
 typedef struct fa_b200_params {
   const void* q;            /* bf16 [B,H,N,d] */
@@ -138,6 +139,33 @@ int64_t fa_b200_decode_workspace_bytes(int32_t B, int32_t H, int32_t kv_len);
 /* Enqueue one decode-attention step on p->stream.  Return values as fa_b200_fwd;
  * FA_B200_ERR_WORKSPACE when the workspace is missing, too small or misaligned. */
 int fa_b200_decode(const fa_b200_decode_params* p);
+
+/* Largest split-KV scratch fa_b200_decode_static can serve, in bytes (the size of the buffer that
+ * is compiled into the library; it occupies this much memory on every GPU that loads the library,
+ * until the process exits). */
+#define FA_B200_STATIC_SCRATCH_BYTES (256 * 1024)
+
+/* fa_b200_decode for callers that must not allocate device memory and have none to lend: the
+ * split-KV partial results go to a fixed buffer that lives inside the library image instead of
+ * p->workspace (p->workspace and p->workspace_bytes are ignored).  Typical callers: a serving
+ * process whose framework has already claimed all device memory for its own pool, so that a
+ * cudaMalloc from a plug-in fails or is forbidden; a request path on which cudaMalloc / cudaFree
+ * are banned because they can synchronise the whole device and stall every other stream; a small
+ * C host with a fixed memory map and no allocator to call.  This function itself calls no
+ * cudaMalloc, cudaFree or other allocating routine.
+ *
+ *   - Problems whose scratch need (fa_b200_decode_workspace_bytes) exceeds
+ *     FA_B200_STATIC_SCRATCH_BYTES are refused with FA_B200_ERR_STATIC_SCRATCH; nothing is
+ *     launched.  (Up to 496 (batch, head) pairs always fit; from 592 pairs on no scratch is used.)
+ *   - The first call on each device looks up the buffer's device address; make that first call
+ *     outside of any stream capture.
+ *   - All calls on a device share the one buffer, and it keeps whatever the previous call left in
+ *     it.  Nothing in it needs clearing -- every partial result is written before it is read --
+ *     but two calls that may run on the GPU at the same time (different streams, different host
+ *     threads) race on it: serialise them, or use fa_b200_decode with separate workspaces.
+ *
+ * Results are identical to fa_b200_decode.  This entry point has no counterpart in the reference. */
+int fa_b200_decode_static(const fa_b200_decode_params* p);
 
 /* FA_B200_ABI_VERSION the library was built with. */
 int fa_b200_abi_version(void);

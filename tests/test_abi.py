@@ -79,7 +79,7 @@ def test_null_params_pointer(fa_lib):
 
 def test_strerror_covers_codes(fa_lib):
     assert _lib.strerror(0) == "ok"
-    for code in range(-12, 0):
+    for code in range(-13, 0):
         assert "unknown" not in _lib.strerror(code)
     assert "watchdog" in _lib.strerror(0x10004)
 

@@ -40,7 +40,7 @@ class FaDecodeParams(ctypes.Structure):
 
 
 EXPORTS = ("fa_b200_fwd", "fa_b200_validate", "fa_b200_strerror", "fa_b200_device_ok",
-           "fa_b200_last_status", "fa_b200_abi_version", "fa_b200_decode", "fa_b200_decode_workspace_bytes")
+           "fa_b200_last_status", "fa_b200_abi_version", "fa_b200_decode", "fa_b200_decode_workspace_bytes", "fa_b200_decode_static")
 
 _lib = None
 
@@ -68,6 +68,8 @@ def load() -> ctypes.CDLL:
     lib.fa_b200_last_status.restype = ctypes.c_int
     lib.fa_b200_decode.argtypes = [ctypes.POINTER(FaDecodeParams)]
     lib.fa_b200_decode.restype = ctypes.c_int
+    lib.fa_b200_decode_static.argtypes = [ctypes.POINTER(FaDecodeParams)]
+    lib.fa_b200_decode_static.restype = ctypes.c_int
     lib.fa_b200_decode_workspace_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
     lib.fa_b200_decode_workspace_bytes.restype = ctypes.c_int64
     lib.fa_b200_abi_version.argtypes = []

@@ -331,6 +331,80 @@ int fa_b200_decode(const fa_b200_decode_params* p) {
   return static_cast<int>(e);
 }
 
+// ----------------------------------------------------------- decode without any allocation
+namespace {
+
+// Split-KV scratch compiled into the library image: one copy per GPU that loads the module.
+// In host code this name is only a handle for the runtime's symbol functions, never a device
+// address; kernels get the address that cudaGetSymbolAddress returns for the current device.
+static __device__ __align__(256) unsigned char g_fa_decode_static_scratch[FA_B200_STATIC_SCRATCH_BYTES];
+
+struct StaticScratchState {
+  std::once_flag once;
+  int error = 0;          // cudaError_t of the address look-up, if it failed
+  float* ptr = nullptr;   // device address of the buffer on this device
+};
+StaticScratchState g_static_scratch[kMaxDevices];
+
+// Runs once per device, with that device current.
+void init_static_scratch(int dev) {
+  StaticScratchState& ss = g_static_scratch[dev];
+  void* addr = nullptr;
+  const cudaError_t e = cudaGetSymbolAddress(&addr, g_fa_decode_static_scratch);
+  if (e != cudaSuccess) { ss.error = static_cast<int>(e); return; }
+  ss.ptr = static_cast<float*>(addr);
+}
+
+}  // namespace
+
+int fa_b200_decode_static(const fa_b200_decode_params* p) {
+  int rc = decode_validate(p);
+  if (rc != FA_B200_OK) return rc;
+  if (p->B == 0 || p->H == 0) return FA_B200_OK;
+  int splits = 1, rows = 0;
+  decode_split(p->B, p->H, p->kv_len, &splits, &rows);
+  if (splits > 1 &&
+      fa_b200_decode_workspace_bytes(p->B, p->H, p->kv_len) > static_cast<int64_t>(FA_B200_STATIC_SCRATCH_BYTES))
+    return FA_B200_ERR_STATIC_SCRATCH;
+
+  DeviceGuard guard(p->device);
+  if (guard.error) return guard.error;
+  DeviceState& st = g_dev[p->device];
+  std::call_once(st.once, init_device, p->device);          // architecture check, no allocation
+  if (st.init_error) return st.init_error;
+  StaticScratchState& ss = g_static_scratch[p->device];
+  std::call_once(ss.once, init_static_scratch, p->device);  // first call on this device only
+  if (ss.error) return ss.error;
+
+  fa::DecodeParams kp;
+  kp.q = static_cast<const __nv_bfloat16*>(p->q);
+  kp.k = static_cast<const __nv_bfloat16*>(p->k_cache);
+  kp.v = static_cast<const __nv_bfloat16*>(p->v_cache);
+  kp.o = static_cast<__nv_bfloat16*>(p->o);
+  kp.lse = p->lse;
+  kp.scratch = ss.ptr;
+  kp.q_sb = p->q_strides[0]; kp.q_sh = p->q_strides[1];
+  kp.o_sb = p->o_strides[0]; kp.o_sh = p->o_strides[1];
+  kp.k_sb = p->k_strides[0]; kp.k_sh = p->k_strides[1]; kp.k_sn = p->k_strides[2];
+  kp.v_sb = p->v_strides[0]; kp.v_sh = p->v_strides[1]; kp.v_sn = p->v_strides[2];
+  kp.B = p->B; kp.H = p->H; kp.kv_len = p->kv_len;
+  kp.splits = splits;
+  kp.rows_per_split = rows;
+  const float scale = p->softmax_scale > 0.0f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(p->d));
+  kp.scale_log2 = scale * 1.4426950408889634f;
+
+  const cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+  const dim3 grid(static_cast<unsigned>(p->B * p->H), static_cast<unsigned>(splits));
+  fa::fa_decode_partial_kernel<<<grid, fa::kDecodeThreads, 0, stream>>>(kp);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (splits > 1) {
+    fa::fa_decode_combine_kernel<<<static_cast<unsigned>(p->B * p->H), 64, 0, stream>>>(kp);
+    e = cudaGetLastError();
+  }
+  return static_cast<int>(e);
+}
+
 int fa_b200_device_ok(int device) {
   if (device < 0) return FA_B200_ERR_DEVICE;
   int count = 0;
@@ -389,6 +463,7 @@ const char* fa_b200_strerror(int code) {
     case FA_B200_ERR_ARCH: return "fa_b200: device is not compute capability 10.x (B200); there is no fallback";
     case FA_B200_ERR_TENSORMAP: return "fa_b200: the driver rejected a TMA tensor map (check strides and sizes)";
     case FA_B200_ERR_DRIVER: return "fa_b200: cuTensorMapEncodeTiled is not available from this driver";
+    case FA_B200_ERR_STATIC_SCRATCH: return "fa_b200: this decode problem needs more split-KV scratch than the built-in buffer holds (FA_B200_STATIC_SCRATCH_BYTES); use fa_b200_decode with a workspace";
     case FA_B200_ERR_WORKSPACE: return "fa_b200: decode workspace is NULL, too small or not 16-byte aligned";
     case FA_B200_ERR_BUILD: return "fa_b200: the kernel image does not match this library's launch configuration; rebuild it";
     default: break;
