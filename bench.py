@@ -412,6 +412,39 @@ def main():
         if cfa.last_status() != 0:
             raise SystemExit("kernel watchdog fired during the decode runs")
 
+    # ---------------------------------------------------------------- the reference's own benchmark
+    # "time for 20 tokens" (model_inference.py:444-465): B=1, a ~70-token prompt, 20 new tokens,
+    # here with random-init weights and random token ids; with the K/V cache + decode kernel, and
+    # with the reference's recompute loop through the prefill kernel.
+    gen = []
+    if not args.no_sweep and rank == 0:
+        from tfg_flashattention_b200 import gpt2
+        for name, seed, gb, gp in (("gpt2-small", 1, 1, 72), ("gpt2-xl", 3, 1, 72), ("gpt2-xl", 3, 8, 900)):
+            cfg = gpt2.gpt2_config(name, impl_type="cuda")
+            model = gpt2.init_random(gpt2.GPTModel(cfg, dtype=torch.bfloat16), seed=seed).cuda().eval()
+            model.prepare_for_inference()
+            prompt = torch.randint(0, cfg["vocab_size"], (gb, gp), generator=torch.Generator().manual_seed(123)).cuda()
+            row = {"model": name, "prompt_tokens": gp, "new_tokens": 20, "batch": gb, "dtype": "bf16",
+                   "note": "B=1 with a short prompt is launch-bound (Python + ~15 launches per layer and token); "
+                           "the cache pays with longer prompts and batches"}
+            for label, use_cache in (("kv_cache_ms", True), ("recompute_ms", False)):
+                gpt2.generate(model, prompt, 20, 1024, temperature=0.0, use_cache=use_cache)
+                torch.cuda.synchronize()
+                times = []
+                for _ in range(3):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    gpt2.generate(model, prompt, 20, 1024, temperature=0.0, use_cache=use_cache)
+                    e1.record()
+                    torch.cuda.synchronize()
+                    times.append(e0.elapsed_time(e1))
+                row[label] = round(statistics.median(times), 2)
+            gen.append(row)
+            del model
+            torch.cuda.empty_cache()
+    if world > 1:
+        barrier(world)
+
     # ---------------------------------------------------------------- CPU baseline (rank 0, N=1 only)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -444,7 +477,8 @@ def main():
             "gpu_launches": args.steps,
             "clocks": clocks,
             "cpu_baseline": cpu,
-            "extra": {"sweep": sweep, "gpt2_prefill": prefill, "decode_step": decode},
+            "extra": {"sweep": sweep, "gpt2_prefill": prefill, "decode_step": decode,
+                      "generate_20_tokens": gen},
         }
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -30,6 +30,11 @@ What differs, on purpose:
     configuration); the default keeps the reference's precision recipe: fp32 everywhere, bf16
     autocast around attention only (:153-154).
 
+  * generation keeps a K/V cache: `generate()` has the reference's signature and sampling rules
+    (:199-228) but runs the prompt once through the prefill kernel and every further token
+    through the single-query decode kernel, instead of re-running the whole prefix per token.
+    `use_cache=False` reproduces the reference's recompute loop (for comparison).
+
 "manual" and "functional" branches are kept for comparison on any device; "cuda" has no fallback.
 """
 from __future__ import annotations
@@ -78,7 +83,10 @@ class MultiHeadAttention(nn.Module):
             self._qkv_b = (None if self.W_query.bias is None else
                            torch.cat([self.W_query.bias, self.W_key.bias, self.W_value.bias], 0).contiguous())
 
-    def forward(self, x):
+    def forward(self, x, kv_cache=None, pos=0):
+        """x [B, n, d_in].  Without a cache: causal attention among the n tokens (prefill).  With
+        kv_cache = (K, V) of shape [B, N_max, H, d]: the new keys/values are written at rows
+        pos .. pos+n-1 and the queries attend rows 0 .. pos+n-1 (causally among themselves)."""
         b, n, _ = x.shape
         h, d = self.num_heads, self.head_dim
         if self._qkv_w is not None and not self.training:
@@ -88,19 +96,32 @@ class MultiHeadAttention(nn.Module):
             q = self.W_query(x).view(b, n, h, d).transpose(1, 2)
             k = self.W_key(x).view(b, n, h, d).transpose(1, 2)
             v = self.W_value(x).view(b, n, h, d).transpose(1, 2)
+        if kv_cache is not None:
+            ck, cv = kv_cache
+            ck[:, pos:pos + n] = k.transpose(1, 2).to(ck.dtype)
+            cv[:, pos:pos + n] = v.transpose(1, 2).to(cv.dtype)
         if self.impl_type == "cuda":
             from . import custom_flash_attn
             if q.dtype != torch.bfloat16:      # outside autocast: the kernel is bf16-only
                 q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
-            ctx = custom_flash_attn.forward(q, k, v).transpose(1, 2)     # [B,N,H,d], dense
-        elif self.impl_type == "manual":
+            if kv_cache is not None and n == 1:
+                ctx = custom_flash_attn.decode(q, ck.transpose(1, 2), cv.transpose(1, 2), pos + 1)
+                ctx = ctx.transpose(1, 2)                                    # [B, 1, H, d]
+            elif pos == 0:
+                ctx = custom_flash_attn.forward(q, k, v).transpose(1, 2)     # [B,N,H,d], dense
+            else:
+                raise NotImplementedError("prefill in several chunks is not supported")
+        elif self.impl_type in ("manual", "functional"):
+            if kv_cache is not None:
+                k = ck[:, :pos + n].transpose(1, 2).to(q.dtype)
+                v = cv[:, :pos + n].transpose(1, 2).to(q.dtype)
+            total = pos + n if kv_cache is not None else n
             attn = q @ k.transpose(-2, -1)
-            mask = torch.triu(torch.ones(n, n, device=x.device), diagonal=1).bool()
+            # query i (absolute position pos + i) sees keys 0 .. pos + i
+            mask = torch.triu(torch.ones(n, total, device=x.device), diagonal=1 + total - n).bool()
             attn.masked_fill_(mask, -torch.inf)
             w = self.dropout(torch.softmax(attn / k.shape[-1] ** 0.5, dim=-1))
             ctx = (w @ v).transpose(1, 2)
-        elif self.impl_type == "functional":
-            ctx = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2)
         else:
             raise ValueError(f"unknown impl_type {self.impl_type!r}")
         ctx = ctx.reshape(b, n, self.d_out)
@@ -146,15 +167,15 @@ class TransformerBlock(nn.Module):
         self.drop_shortcut = nn.Dropout(cfg["drop_rate"])
         self.autocast_attention = autocast_attention
 
-    def forward(self, x):
+    def forward(self, x, kv_cache=None, pos=0):
         shortcut = x
         h = self.norm1(x)
         if self.autocast_attention and x.is_cuda and x.dtype == torch.float32:
             with torch.autocast(device_type="cuda", dtype=torch.bfloat16):   # as the reference, :153
-                h = self.att(h)
+                h = self.att(h, kv_cache, pos)
             h = h.to(x.dtype)
         else:
-            h = self.att(h)
+            h = self.att(h, kv_cache, pos)
         x = self.drop_shortcut(h) + shortcut
         shortcut = x
         x = self.drop_shortcut(self.ff(self.norm2(x))) + shortcut
@@ -186,16 +207,69 @@ class GPTModel(nn.Module):
             self._head_w = F.pad(w, (0, 0, 0, pad)).contiguous() if pad else None
         return self
 
-    def forward(self, in_idx, last_token_only=False):
+    def allocate_kv_cache(self, batch, max_len=None, dtype=None):
+        """One (K, V) pair of [B, N_max, H, d] tensors per layer, in the model's device; bf16 when
+        the attention kernel is used (it reads the cache in place)."""
+        dev = self.tok_emb.weight.device
+        h = self.cfg["n_heads"]
+        d = self.cfg["emb_dim"] // h
+        n_max = self.cfg["context_length"] if max_len is None else max_len
+        if dtype is None:
+            dtype = torch.bfloat16 if self.cfg["impl_type"] == "cuda" else self.tok_emb.weight.dtype
+        return [(torch.zeros(batch, n_max, h, d, dtype=dtype, device=dev),
+                 torch.zeros(batch, n_max, h, d, dtype=dtype, device=dev))
+                for _ in range(self.cfg["n_layers"])]
+
+    def forward(self, in_idx, last_token_only=False, kv_caches=None, pos=0):
         _, n = in_idx.shape
-        x = self.tok_emb(in_idx) + self.pos_emb(torch.arange(n, device=in_idx.device))
-        x = self.trf_blocks(self.drop_emb(x))
+        x = self.tok_emb(in_idx) + self.pos_emb(torch.arange(pos, pos + n, device=in_idx.device))
+        x = self.drop_emb(x)
+        if kv_caches is None:
+            x = self.trf_blocks(x)
+        else:
+            for blk, cache in zip(self.trf_blocks, kv_caches):
+                x = blk(x, cache, pos)
         x = self.final_norm(x)
         if last_token_only:           # what generate() consumes (model_inference.py:206)
             x = x[:, -1:, :]
         if self._head_w is not None and not self.training:
             return F.linear(x, self._head_w)[..., :self.out_head.weight.shape[0]]
         return self.out_head(x)
+
+
+@torch.no_grad()
+def generate(model, idx, max_new_tokens, context_size, temperature=1.0, top_k=None, eos_id=None,
+             use_cache=True, generator=None):
+    """The reference's generate() (model_inference.py:199-228): same arguments, same top-k /
+    temperature / multinomial-or-argmax rules, same stop at eos_id.  With use_cache=True the
+    prompt is run once and each new token costs one single-token forward against the K/V cache;
+    with use_cache=False every token re-runs `idx[:, -context_size:]` as the reference does."""
+    caches = None
+    pos = 0
+    if use_cache:
+        if idx.shape[1] + max_new_tokens > context_size:
+            raise ValueError("prompt + new tokens exceed the context length (the cache does not slide)")
+        caches = model.allocate_kv_cache(idx.shape[0], context_size)
+    for step in range(max_new_tokens):
+        if use_cache:
+            inp = idx if step == 0 else idx[:, -1:]
+            logits = model(inp, last_token_only=True, kv_caches=caches, pos=pos)
+            pos += inp.shape[1]
+        else:
+            logits = model(idx[:, -context_size:], last_token_only=True)
+        logits = logits[:, -1, :].float()
+        if top_k is not None:
+            top_logits, _ = torch.topk(logits, top_k)
+            logits = torch.where(logits < top_logits[:, -1:], torch.full_like(logits, -torch.inf), logits)
+        if temperature > 0.0:
+            probs = torch.softmax(logits / temperature, dim=-1)
+            idx_next = torch.multinomial(probs, num_samples=1, generator=generator)
+        else:
+            idx_next = torch.argmax(logits, dim=-1, keepdim=True)
+        if eos_id is not None and idx.shape[0] == 1 and int(idx_next) == eos_id:   # as the reference, :224
+            break
+        idx = torch.cat((idx, idx_next), dim=1)
+    return idx
 
 
 def init_random(model: GPTModel, seed: int, std: float = 0.02) -> GPTModel:
