@@ -264,6 +264,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-sweep", action="store_true", help="skip the extra configurations")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--decode-case", default=None, metavar="B,H,kv_len",
+                    help="time only this decode step (small runs for profilers); prints a short line")
     ap.add_argument("--case", default=None, metavar="B,H,N,causal",
                     help="time only this attention problem (small runs for profilers); prints a short line")
     args = ap.parse_args()
@@ -280,6 +282,29 @@ def main():
     torch.cuda.set_device(local)
     from tfg_flashattention_b200 import custom_flash_attn as cfa
     peaks = load_peaks()
+
+    if args.decode_case:
+        db, dh, dn = (int(x) for x in args.decode_case.split(","))
+        g = torch.Generator(device="cuda").manual_seed(11)
+        dq = torch.randn(db, dh, 64, device="cuda", generator=g).bfloat16()
+        n_sets = max(1, min(8, int(400e6 // (2 * db * dh * dn * 128)) + 1))
+        caches = [(torch.randn(db, dh, dn, 64, device="cuda", generator=g).bfloat16(),
+                   torch.randn(db, dh, dn, 64, device="cuda", generator=g).bfloat16()) for _ in range(n_sets)]
+        do = torch.empty_like(dq)
+        for i in range(args.warmup):
+            cfa.decode(dq, *caches[i % n_sets], dn, out=do)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            cfa.decode(dq, *caches[i % n_sets], dn, out=do)
+        e1.record()
+        torch.cuda.synchronize()
+        dms = e0.elapsed_time(e1) / args.steps
+        print(json.dumps({"decode_case": args.decode_case, "us_per_step": dms * 1e3,
+                          "gbs": 2.0 * db * dh * dn * 128 / (dms * 1e-3) / 1e9,
+                          "status": cfa.last_status()}), flush=True)
+        return
 
     if args.case:
         cb, ch, cn, cc = (int(x) for x in args.case.split(","))
