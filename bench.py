@@ -220,6 +220,15 @@ def cpu_attention_sample(w, reps, threads):
     return flops / statistics.median(times) / 1e12, bs, times
 
 
+def bench_config(w):
+    """The workload description both arms print."""
+    return {"workload": "gpt2-xl-layer-attention (config 4 attention shape)",
+            "B_per_gpu": w.B, "H": w.H, "N": w.N, "d": w.d, "causal": True,
+            "flops_convention": "causal-adjusted 2*B*H*N^2*d",
+            "l2_policy": "inputs (420 MB per GPU) larger than L2 (126 MB)",
+            "sharding": "independent (batch, head) problems per GPU, no collective"}
+
+
 def run_reference(args, w):
     """The reference arm: the reference's standard-PyTorch attention (CPU port in oracle/) on all
     host threads; one bounded sample per step."""
@@ -247,8 +256,7 @@ def run_reference(args, w):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": w.name, "B_per_gpu": w.B, "H": w.H, "N": w.N, "d": w.d, "causal": True,
-                   "note": "CPU implementation; runs on rank 0 only, value does not scale with --gpus"},
+        "config": dict(bench_config(w), note="CPU implementation; runs on rank 0 only, value does not scale with --gpus"),
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -484,11 +492,7 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "gpt2-xl-layer-attention (config 4 attention shape)",
-                       "B_per_gpu": w.B, "H": w.H, "N": w.N, "d": w.d, "causal": True,
-                       "flops_convention": "causal-adjusted 2*B*H*N^2*d",
-                       "l2_policy": "inputs (420 MB per GPU) larger than L2 (126 MB)",
-                       "sharding": "independent (batch, head) problems per GPU, no collective"},
+            "config": bench_config(w),
             "tflops_per_gpu": per_gpu,
             "frac_of_bf16_peak": per_gpu / peaks["bf16_tflops"],
             "frac_of_bf16_peak_sustained": (per_gpu / peaks["bf16_tflops_sustained"]) if peaks["bf16_tflops_sustained"] else None,
