@@ -62,6 +62,10 @@ static_assert(kSoftmaxRegs % 8 == 0 && kOtherRegs % 8 == 0 && kOtherRegs >= 24, 
 constexpr uint32_t kTmemCols = 256;    // two resident CTAs share the SM's 512 columns
 constexpr uint32_t kTmemS = 0, kTmemP = 128, kTmemO = 192;
 constexpr float kRescaleThresholdLog2 = 8.0f;
+#ifndef FA_POLY_PER_EIGHT
+#define FA_POLY_PER_EIGHT 2
+#endif
+constexpr int kPolyPerEight = FA_POLY_PER_EIGHT;  // exponentials per 8 evaluated on the FMA pipe
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
 
 // watchdog codes (status word 0); low byte tells which wait ran out
@@ -86,6 +90,7 @@ struct __align__(1024) SharedStorage {
   uint64_t o_free;               // the epilogue has read O: the next item may overwrite it
   uint32_t tmem_base;
   uint32_t abort;
+  float2 owed[kBlockM];          // per row of a finished item: {1 / l, m * c + log2 l} for its epilogue
 };
 constexpr int kSmemBytes = sizeof(SharedStorage) + 1024;  // + slack to align the base to 1024
 static_assert(kCtasPerSm * (kSmemBytes + 1024) <= 227 * 1024, "two CTAs must fit in one SM");
@@ -423,10 +428,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     const uint32_t bar_s_free = smem_u32(&sm.s_free);
     const uint32_t bar_p = smem_u32(&sm.p_full);
     const uint32_t bar_o = smem_u32(&sm.o_full);
-    const uint32_t bar_o_free = smem_u32(&sm.o_free);
-    // this thread's row of the staging tile; 16-byte chunk c goes to position c ^ (r & 7)
-    // (the 128-byte swizzle the TMA store expects)
-    const uint32_t stage_row = smem_u32(sm.o_stage) + r * 128;
     constexpr uint32_t kNegInf = 0xff800000u;
 
     bool ok = true;
@@ -436,15 +437,32 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     // A finished item whose epilogue is still owed.  It is run in the middle of the NEXT item's
     // first tile (after that tile's P is stored, before the issuer is told about it): by then the
     // last O += P V of the finished item has long completed, so nobody sits waiting for it.
-    bool owed = false;
-    int owed_q_row = 0, owed_h = 0, owed_b = 0, owed_n = 0;
-    float owed_m = 0.f, owed_l = 1.f;
-
+    // What the epilogue needs of the finished item waits in shared memory, not in registers that
+    // would stay live through the hot loop: each thread parks its row's {1 / l, m * c + log2 l},
+    // and the item itself is decoded again from its index.
     // O / l -> bf16 -> swizzled staging tile -> TMA store; LSE.  Reads O of the owed item.
-    auto epilogue = [&]() -> bool {
+    auto epilogue = [&](const int owed_n) -> bool {
+      Item ow;
+      get_item(owed_n, ow);
+      const float2 parked = sm.owed[r];
+      const uint32_t bar_o_free = smem_u32(&sm.o_free);
+      // this thread's row of the staging tile; 16-byte chunk c goes to position c ^ (r & 7)
+      // (the 128-byte swizzle the TMA store expects)
+      const uint32_t stage_row = smem_u32(sm.o_stage) + r * 128;
+      const int owed_q_row = ow.q_row, owed_h = ow.h, owed_b = ow.b;
       tc_fence_after();
-      uint32_t ov[kHeadDim];
-      tmem_ld_x64(t_o, ov);
+      // O / l -> bf16 while loading, 32 columns at a time (keeps the register peak low: the
+      // persistent kernel runs this in the middle of a tile)
+      const float inv_l = parked.x;
+      uint32_t ob[kHeadDim / 2];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t ov[32];
+        tmem_ld_x32(t_o + 32 * half, ov);
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          ob[16 * half + i] = pack_bf16(__uint_as_float(ov[2 * i]) * inv_l, __uint_as_float(ov[2 * i + 1]) * inv_l);
+      }
       // O is in registers: the issuer may start the next item's accumulation
       tc_fence_before();
       __syncwarp();
@@ -454,14 +472,13 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       // rewritten (it was issued a whole work item ago).
       if (lane == 0) tma_store_wait_read<0>();
       __syncwarp();
-      const float inv_l = 1.0f / owed_l;
 #pragma unroll
       for (int ck = 0; ck < 8; ++ck) {
         uint4 wv;
-        wv.x = pack_bf16(__uint_as_float(ov[8 * ck + 0]) * inv_l, __uint_as_float(ov[8 * ck + 1]) * inv_l);
-        wv.y = pack_bf16(__uint_as_float(ov[8 * ck + 2]) * inv_l, __uint_as_float(ov[8 * ck + 3]) * inv_l);
-        wv.z = pack_bf16(__uint_as_float(ov[8 * ck + 4]) * inv_l, __uint_as_float(ov[8 * ck + 5]) * inv_l);
-        wv.w = pack_bf16(__uint_as_float(ov[8 * ck + 6]) * inv_l, __uint_as_float(ov[8 * ck + 7]) * inv_l);
+        wv.x = ob[4 * ck + 0];
+        wv.y = ob[4 * ck + 1];
+        wv.z = ob[4 * ck + 2];
+        wv.w = ob[4 * ck + 3];
         st_shared_v4(stage_row + ((ck ^ (r & 7)) << 4), wv);
       }
       fence_proxy_async_smem();     // generic-proxy writes -> visible to the TMA engine
@@ -475,9 +492,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       if (p.lse != nullptr && row < p.N) {
         // ln(sum_j exp(scale * s_j)) = ln2 * (m_ref * c + log2(l))
         p.lse[((long long)owed_b * p.H + owed_h) * p.N + row] =
-            0.6931471805599453f * (owed_m * c + log2f(owed_l));
+            0.6931471805599453f * parked.y;
       }
-      owed = false;
       return true;
     };
 
@@ -574,31 +590,49 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         }
 
         const float neg_mc_all = -m_ref * c;
-        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+        const uint64_t c2 = pack_f32x2(c, c);
+        uint64_t lsum0 = 0ull, lsum1 = 0ull;   // two packed pairs of partial row sums
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {   // 32 scores -> 16 packed registers -> one TMEM store
           uint32_t pk[16];
           const float neg_mc = ch >= first_masked_chunk ? -CUDART_INF_F : neg_mc_all;  // exp2(-inf) = 0
+          const uint64_t neg_mc2 = pack_f32x2(neg_mc, neg_mc);
 #pragma unroll
           for (int k = 0; k < 32; k += 4) {
             const int o = 32 * ch + k;
-            const float p0 = ex2_approx(fmaf(__uint_as_float(sv[o + 0]), c, neg_mc));
-            const float p1 = ex2_approx(fmaf(__uint_as_float(sv[o + 1]), c, neg_mc));
-            const float p2 = ex2_approx(fmaf(__uint_as_float(sv[o + 2]), c, neg_mc));
-            const float p3 = ex2_approx(fmaf(__uint_as_float(sv[o + 3]), c, neg_mc));
-            l0 += p0; l1 += p1; l2 += p2; l3 += p3;
+            float x0, x1, x2, x3;
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(sv[o + 0]), __uint_as_float(sv[o + 1])), c2, neg_mc2), x0, x1);
+            const uint64_t xb = fma_f32x2(pack_f32x2(__uint_as_float(sv[o + 2]), __uint_as_float(sv[o + 3])), c2, neg_mc2);
+            unpack_f32x2(xb, x2, x3);
+            const float p0 = ex2_approx(x0);
+            const float p1 = ex2_approx(x1);
+            float p2, p3;
+            if ((kPolyPerEight >= 2 && (k % 8) == 4) || (kPolyPerEight >= 4 && (k % 8) == 0) ||
+                (kPolyPerEight == 3 && (k % 16) == 8)) {
+              exp2_poly_x2(x2, x3, p2, p3);
+            } else {
+              p2 = ex2_approx(x2);
+              p3 = ex2_approx(x3);
+            }
+            lsum0 = add_f32x2(lsum0, pack_f32x2(p0, p1));
+            lsum1 = add_f32x2(lsum1, pack_f32x2(p2, p3));
             pk[k / 2 + 0] = pack_bf16(p0, p1);
             pk[k / 2 + 1] = pack_bf16(p2, p3);
           }
           tmem_st_x16(t_p + 16 * ch, pk);
         }
-        l += (l0 + l1) + (l2 + l3);
+        {
+          float l0, l1, l2, l3;
+          unpack_f32x2(lsum0, l0, l1);
+          unpack_f32x2(lsum1, l2, l3);
+          l += (l0 + l1) + (l2 + l3);
+        }
         tmem_wait_st();
 
         // the epilogue owed to the previous item: its O is final (the wait above covered its last
         // PV) and must be read before the issuer accumulates this item's first P V into O
-        if (kPersistent && owed) {
-          ok = epilogue();
+        if (kPersistent && j == 0 && n > 0) {
+          ok = epilogue(n - 1);
           if (!ok) break;
         }
 
@@ -607,14 +641,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         if (lane == 0) mbar_arrive(bar_p);
       }
       if (!ok) break;
-      owed = true;
-      owed_q_row = w.q_row; owed_h = w.h; owed_b = w.b; owed_n = n;
-      owed_m = m_ref; owed_l = l;
+      sm.owed[r] = make_float2(1.0f / l, m_ref * c + log2f(l));   // read back by this same thread
     }
     // the last item's epilogue
-    if (ok && owed) {
+    if (ok && n > 0) {
       ok = wait_bar_warp(bar_o, (g - 1) & 1, watch, kWaitOFull);
-      if (ok) ok = epilogue();
+      if (ok) ok = epilogue(n - 1);
     }
     // each warp's last TMA store must have read its slab before shared memory goes away
     if (lane == 0) tma_store_wait_read<0>();

@@ -204,6 +204,47 @@ __device__ __forceinline__ float lg2_approx(float x) {
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Packed pairs of fp32 in one 64-bit register: one issue slot does two lanes' worth of FMA / ADD.
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t sub_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// 2^x for two values on the FMA pipe (no MUFU): x is clamped to >= -126, split into
+// round(x) + f with f in [-0.5, 0.5] by the 1.5 * 2^23 shift, 2^f is a cubic (relative error
+// below 1e-4, far under the bf16 rounding of P that follows) and round(x) goes into the exponent.
+__device__ __forceinline__ void exp2_poly_x2(float x0, float x1, float& y0, float& y1) {
+  const uint64_t shift = pack_f32x2(12582912.f, 12582912.f);
+  const uint64_t x = pack_f32x2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const uint64_t t = add_f32x2(x, shift);
+  const uint64_t f = sub_f32x2(x, sub_f32x2(t, shift));
+  uint64_t q = fma_f32x2(pack_f32x2(0.0551716685f, 0.0551716685f), f, pack_f32x2(0.2426111251f, 0.2426111251f));
+  q = fma_f32x2(q, f, pack_f32x2(0.6932609677f, 0.6932609677f));
+  q = fma_f32x2(q, f, pack_f32x2(0.9999280572f, 0.9999280572f));
+  float t0, t1, q0, q1;
+  unpack_f32x2(t, t0, t1);
+  unpack_f32x2(q, q0, q1);
+  y0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+  y1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+}
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float y;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));

@@ -35,6 +35,8 @@ What differs, on purpose:
     through the single-query decode kernel, instead of re-running the whole prefix per token.
     `use_cache=False` reproduces the reference's recompute loop (for comparison).
 
+  * `load_weights_into_gpt(gpt, params)` (:313-376) lives in `checkpoint.py`.
+
 "manual" and "functional" branches are kept for comparison on any device; "cuda" has no fallback.
 """
 from __future__ import annotations
@@ -205,6 +207,13 @@ class GPTModel(nn.Module):
         pad = (-w.shape[0]) % 64
         with torch.no_grad():
             self._head_w = F.pad(w, (0, 0, 0, pad)).contiguous() if pad else None
+        return self
+
+    def invalidate_inference_cache(self):
+        """Drop the derived tensors of `prepare_for_inference` (after the parameters changed)."""
+        for blk in self.trf_blocks:
+            blk.att._qkv_w = blk.att._qkv_b = None
+        self._head_w = None
         return self
 
     def allocate_kv_cache(self, batch, max_len=None, dtype=None):
