@@ -383,29 +383,39 @@ def main():
             model.prepare_for_inference()     # fused QKV GEMM, vocabulary padded to a multiple of 64
             ids = torch.randint(0, cfg["vocab_size"], (batch, 1024),
                                 generator=torch.Generator().manual_seed(seed + rank)).cuda()
-            with torch.no_grad():
-                for _ in range(3):
-                    model(ids)
-                barrier(world)
+            def timed_forwards(fwd):
                 # one event pair per forward; the median is robust against a first-use stall
                 # (cuBLAS kernel loading, allocator growth) landing inside the timed steps
+                for _ in range(3):
+                    fwd(ids)
+                barrier(world)
                 evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
                        for _ in range(steps)]
                 for e0, e1 in evs:
                     e0.record()
-                    logits = model(ids)
+                    fwd(ids)
                     e1.record()
                 barrier(world)
-            times = [e0.elapsed_time(e1) for e0, e1 in evs]
-            pms = max_over_ranks(statistics.median(times), world)
-            pms_mean = max_over_ranks(sum(times) / len(times), world)
+                times = [e0.elapsed_time(e1) for e0, e1 in evs]
+                return (max_over_ranks(statistics.median(times), world),
+                        max_over_ranks(sum(times) / len(times), world))
+            with torch.no_grad():
+                eager_ms, _ = timed_forwards(model)
+                # the same forward recorded once as a CUDA graph and replayed: every step still
+                # copies the token ids in and runs all kernels, only the host launch gaps go
+                graphed = model.capture_prefill(batch, 1024)
+                pms, pms_mean = timed_forwards(graphed)
+                logits = graphed(ids)
             tok_s = world * batch * 1024 / (pms * 1e-3)
             prefill.append({"model": name, "batch_per_gpu": batch, "seq_len": 1024, "dtype": "bf16",
-                            "weights": f"random N(0,0.02) seed {seed}", "ms_per_forward": round(pms, 3), "ms_per_forward_mean": round(pms_mean, 3), "timing": f"median of {steps} forwards, CUDA events",
+                            "weights": f"random N(0,0.02) seed {seed}", "ms_per_forward": round(pms, 3), "ms_per_forward_mean": round(pms_mean, 3), "timing": f"median of {steps} forwards, CUDA events; one CUDA-graph replay per forward",
+                            "ms_per_forward_eager": round(eager_ms, 3),
                             "tokens_per_s": round(tok_s, 1),
                             "model_tflops_per_gpu": round(tok_s / world * gpt2.prefill_flops_per_token(cfg, 1024) / 1e12, 1),
                             "attention": "fa::fa_fwd_kernel on strided [B,N,H,d] views, every layer",
+                            "block_ops": "fa::fa_add_layernorm_kernel (residual add + LayerNorm), GELU in the cuBLASLt GEMM epilogue, fused QKV GEMM",
                             "logits": "all positions"})
+            del graphed
             del model, ids, logits
             torch.cuda.empty_cache()
         if cfa.last_status() != 0:

@@ -167,6 +167,37 @@ int fa_b200_decode(const fa_b200_decode_params* p);
  * Results are identical to fa_b200_decode.  This entry point has no counterpart in the reference. */
 int fa_b200_decode_static(const fa_b200_decode_params* p);
 
+/* Residual add + LayerNorm in one pass (bf16 in / out, fp32 arithmetic), for the transformer block
+ * around the attention call:
+ *
+ *     s = a + resid                         resid may be NULL (plain LayerNorm)
+ *     if (sum_out) sum_out = s              the new residual stream, rounded to bf16
+ *     norm_out = (s - mean) / sqrt(var + eps) * scale + shift      (biased variance, per row)
+ *
+ * Replaces the reference's LayerNorm.forward (src/py/model_inference.py:102-107, about ten
+ * elementwise kernels) together with the shortcut additions of TransformerBlock.forward
+ * (:156, :163).  All matrices are dense row-major [rows, cols] bf16, scale / shift [cols] bf16;
+ * every pointer 16-byte aligned; cols a positive multiple of 8 and at most 2048; rows >= 0
+ * (rows == 0 is a no-op).  When sum_out is given, the row that is normalised is the bf16-rounded
+ * sum, i.e. exactly what a later reader of sum_out sees.  sum_out may alias a or resid; norm_out
+ * may alias a.  Asynchronous on p->stream.  Errors: FA_B200_ERR_NULL, _SHAPE, _ALIGN, _DEVICE,
+ * _ARCH, or a positive cudaError_t. */
+typedef struct fa_b200_add_layernorm_params {
+  const void* a;
+  const void* resid;      /* or NULL */
+  const void* scale;
+  const void* shift;
+  void* sum_out;          /* or NULL */
+  void* norm_out;
+  int64_t rows;
+  int32_t cols;
+  float eps;
+  int32_t device;
+  void* stream;
+} fa_b200_add_layernorm_params;
+
+int fa_b200_add_layernorm(const fa_b200_add_layernorm_params* p);
+
 /* FA_B200_ABI_VERSION the library was built with. */
 int fa_b200_abi_version(void);
 

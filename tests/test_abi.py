@@ -115,3 +115,26 @@ def test_python_shim_rejects_cpu_and_dtype():
     q = torch.zeros(1, 1, 8, 64, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
         custom_flash_attn.forward(q, q, q)
+
+
+def test_add_layernorm_rejects_before_any_cuda_call(fa_lib):
+    def params(**kw):
+        p = _lib.FaAddLnParams()
+        p.a, p.resid, p.scale, p.shift = 0x1000, 0x2000, 0x3000, 0x4000
+        p.sum_out, p.norm_out = 0x5000, 0x6000
+        p.rows, p.cols, p.eps, p.device, p.stream = 4, 768, 1e-5, 0, None
+        for k, v in kw.items():
+            setattr(p, k, v)
+        return p
+    call = lambda p: fa_lib.fa_b200_add_layernorm(ctypes.byref(p))
+    assert fa_lib.fa_b200_add_layernorm(None) == -1
+    assert call(params(a=None)) == -1
+    assert call(params(norm_out=None)) == -1
+    assert call(params(cols=0)) == -3
+    assert call(params(cols=770)) == -3            # not a multiple of 8
+    assert call(params(cols=2056)) == -3           # more than 2048 columns
+    assert call(params(rows=-1)) == -3
+    assert call(params(resid=0x2008)) == -5
+    assert call(params(eps=-1.0)) == -6
+    assert call(params(device=-2)) == -7
+    assert call(params(rows=0)) == 0               # nothing to do, nothing launched

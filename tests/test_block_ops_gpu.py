@@ -1,0 +1,88 @@
+"""Residual add + LayerNorm kernel against the reference's LayerNorm arithmetic in fp32."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _reference(a, resid, scale, shift, eps):
+    """model_inference.py:102-107 (mean, var(unbiased=False), eps, scale, shift) on the bf16-rounded
+    sum, in fp32."""
+    s = a.float() + (resid.float() if resid is not None else 0.0)
+    s = s.bfloat16().float() if resid is not None else s
+    mean = s.mean(dim=-1, keepdim=True)
+    var = s.var(dim=-1, keepdim=True, unbiased=False)
+    return s, (s - mean) / torch.sqrt(var + eps) * scale.float() + shift.float()
+
+
+@pytest.mark.parametrize("cols", [8, 64, 768, 1024, 1280, 1600, 2048])
+@pytest.mark.parametrize("rows", [1, 7, 1000])
+@pytest.mark.parametrize("with_resid", [False, True])
+def test_add_layernorm_matches_fp32(fa_lib, rows, cols, with_resid):
+    from tfg_flashattention_b200.block_ops import add_layernorm
+    g = torch.Generator(device="cuda").manual_seed(rows * 10000 + cols)
+    rnd = lambda *s: torch.randn(*s, device="cuda", generator=g)
+    a = (rnd(rows, cols) * 2 + 0.5).bfloat16()
+    resid = (rnd(rows, cols) * 3 - 1).bfloat16() if with_resid else None
+    scale, shift = (1 + 0.2 * rnd(cols)).bfloat16(), (0.3 * rnd(cols)).bfloat16()
+    out = add_layernorm(a, resid, scale, shift, 1e-5)
+    s_ref, y_ref = _reference(a, resid, scale, shift, 1e-5)
+    if with_resid:
+        s, y = out
+        assert torch.equal(s, s_ref.bfloat16())          # the sum is bit-exact
+    else:
+        y = out
+    # one bf16 rounding of a value of magnitude <= ~8: half an ulp of 2^-5, plus fp32 noise
+    err = (y.float() - y_ref).abs()
+    assert (err <= 2.0 ** -8 * y_ref.abs().clamp_min(1.0) + 1e-3).all(), err.max().item()
+
+
+def test_add_layernorm_in_place_and_3d(fa_lib):
+    from tfg_flashattention_b200.block_ops import add_layernorm
+    torch.manual_seed(0)
+    a = torch.randn(2, 5, 1600, device="cuda").bfloat16()
+    x = torch.randn(2, 5, 1600, device="cuda").bfloat16()
+    scale, shift = torch.ones(1600, device="cuda").bfloat16(), torch.zeros(1600, device="cuda").bfloat16()
+    s0, y0 = add_layernorm(a, x, scale, shift)
+    x_alias = x.clone()
+    s1, y1 = add_layernorm(a, x_alias, scale, shift, sum_out=x_alias)     # residual stream updated in place
+    assert s1.data_ptr() == x_alias.data_ptr()
+    assert torch.equal(s0, s1) and torch.equal(y0, y1)
+    # without a kept sum the row is normalised before any rounding: equal up to that rounding
+    y2 = add_layernorm(a, x, scale, shift, return_sum=False)
+    torch.testing.assert_close(y2.float(), y0.float(), rtol=0, atol=0.05)
+
+
+def test_add_layernorm_rejects(fa_lib):
+    from tfg_flashattention_b200.block_ops import add_layernorm
+    ok = torch.zeros(4, 64, device="cuda").bfloat16()
+    w = torch.ones(64, device="cuda").bfloat16()
+    with pytest.raises(RuntimeError):
+        add_layernorm(ok.float(), None, w, w)
+    with pytest.raises(RuntimeError):
+        add_layernorm(ok[:, :32], None, w[:32], w[:32])                    # not contiguous
+    with pytest.raises(RuntimeError):
+        add_layernorm(ok, ok[:2], w, w)
+    bad = torch.zeros(4, 2056, device="cuda").bfloat16()
+    with pytest.raises(RuntimeError, match="fa_b200"):
+        add_layernorm(bad, None, torch.ones(2056, device="cuda").bfloat16(), torch.ones(2056, device="cuda").bfloat16())
+
+
+def test_fused_block_path_equals_module_by_module_path(fa_lib):
+    """GPTModel with the fused add+LayerNorm / GELU-epilogue path against the same bf16 model run
+    block by block through torch's layer_norm, add and gelu."""
+    from tfg_flashattention_b200 import gpt2
+    cfg = {"vocab_size": 503, "context_length": 256, "emb_dim": 256, "n_heads": 4, "n_layers": 3,
+           "drop_rate": 0.0, "qkv_bias": True, "impl_type": "cuda"}
+    model = gpt2.init_random(gpt2.GPTModel(cfg, dtype=torch.bfloat16), seed=5, std=0.05).cuda().eval()
+    ids = torch.randint(0, cfg["vocab_size"], (3, 200), device="cuda")
+    with torch.no_grad():
+        plain = model(ids).float()
+        model.prepare_for_inference()
+        assert model._fused_blocks
+        fused = model(ids).float()
+        last = model(ids, last_token_only=True).float()
+    scale = plain.abs().max().item()
+    assert (fused - plain).abs().max().item() <= 0.03 * scale      # bf16 rounding at different places
+    assert (fused - plain).abs().mean().item() <= 0.004 * scale
+    torch.testing.assert_close(last, fused[:, -1:, :], rtol=0, atol=0.02 * scale)

@@ -39,8 +39,19 @@ class FaDecodeParams(ctypes.Structure):
     ]
 
 
+class FaAddLnParams(ctypes.Structure):
+    """struct fa_b200_add_layernorm_params (include/fa_b200.h)."""
+    _fields_ = [
+        ("a", ctypes.c_void_p), ("resid", ctypes.c_void_p), ("scale", ctypes.c_void_p),
+        ("shift", ctypes.c_void_p), ("sum_out", ctypes.c_void_p), ("norm_out", ctypes.c_void_p),
+        ("rows", ctypes.c_int64), ("cols", ctypes.c_int32), ("eps", ctypes.c_float),
+        ("device", ctypes.c_int32), ("stream", ctypes.c_void_p),
+    ]
+
+
 EXPORTS = ("fa_b200_fwd", "fa_b200_validate", "fa_b200_strerror", "fa_b200_device_ok",
-           "fa_b200_last_status", "fa_b200_abi_version", "fa_b200_decode", "fa_b200_decode_workspace_bytes", "fa_b200_decode_static")
+           "fa_b200_last_status", "fa_b200_abi_version", "fa_b200_decode", "fa_b200_decode_workspace_bytes", "fa_b200_decode_static",
+           "fa_b200_add_layernorm")
 
 _lib = None
 
@@ -72,6 +83,8 @@ def load() -> ctypes.CDLL:
     lib.fa_b200_decode_static.restype = ctypes.c_int
     lib.fa_b200_decode_workspace_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
     lib.fa_b200_decode_workspace_bytes.restype = ctypes.c_int64
+    lib.fa_b200_add_layernorm.argtypes = [ctypes.POINTER(FaAddLnParams)]
+    lib.fa_b200_add_layernorm.restype = ctypes.c_int
     lib.fa_b200_abi_version.argtypes = []
     lib.fa_b200_abi_version.restype = ctypes.c_int
     if lib.fa_b200_abi_version() != ABI_VERSION:

@@ -1,0 +1,58 @@
+"""The element-wise work of a transformer block around the attention call, as single kernels.
+
+`add_layernorm` is the reference's LayerNorm.forward (src/py/model_inference.py:102-107) fused
+with the shortcut addition that precedes it (TransformerBlock.forward, :156 and :163); the
+arithmetic is `fa_b200_add_layernorm` in libfa_b200.so (include/fa_b200.h).  CUDA bf16 only, no
+fallback: the GPT-2 harness uses it on its bf16 inference path and keeps the torch ops elsewhere.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+__all__ = ["add_layernorm"]
+
+
+def _dense2d(t: torch.Tensor, name: str, cols: int) -> torch.Tensor:
+    if not (isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.bfloat16):
+        raise RuntimeError(f"{name} must be a CUDA bfloat16 tensor")
+    if t.shape[-1] != cols or not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous with {cols} columns")
+    return t
+
+
+def add_layernorm(a, resid, scale, shift, eps: float = 1e-5, return_sum: bool = True,
+                  sum_out=None, norm_out=None):
+    """`s = a + resid` (resid may be None), `y = LayerNorm(s) * scale + shift` over the last
+    dimension, one pass.  Returns `(s, y)` when `return_sum` and a residual is given, else `y`.
+    The normalised row is the bf16-rounded sum (what a later reader of `s` sees)."""
+    cols = a.shape[-1]
+    _dense2d(a, "a", cols)
+    if resid is not None:
+        _dense2d(resid, "resid", cols)
+        if resid.shape != a.shape:
+            raise RuntimeError("a and resid must have the same shape")
+    for t, name in ((scale, "scale"), (shift, "shift")):
+        _dense2d(t, name, cols)
+        if t.numel() != cols:
+            raise RuntimeError(f"{name} must have {cols} elements")
+    keep = return_sum and resid is not None
+    if keep and sum_out is None:
+        sum_out = torch.empty_like(a)
+    if norm_out is None:
+        norm_out = torch.empty_like(a)
+    p = _lib.FaAddLnParams()
+    p.a, p.resid = a.data_ptr(), (resid.data_ptr() if resid is not None else None)
+    p.scale, p.shift = scale.data_ptr(), shift.data_ptr()
+    p.sum_out = sum_out.data_ptr() if keep else None
+    p.norm_out = norm_out.data_ptr()
+    p.rows, p.cols, p.eps = a.numel() // cols if cols else 0, cols, eps
+    p.device = a.device.index
+    p.stream = torch.cuda.current_stream(a.device).cuda_stream
+    rc = _lib.load().fa_b200_add_layernorm(ctypes.byref(p))
+    if rc != 0:
+        raise RuntimeError(_lib.strerror(rc))
+    return (sum_out, norm_out) if keep else norm_out

@@ -11,6 +11,7 @@
 #include <mutex>
 
 #include "../../include/fa_b200.h"
+#include "add_layernorm_sm100.cuh"
 #include "fa_decode_sm100.cuh"
 #include "fa_fwd_sm100.cuh"
 
@@ -435,6 +436,66 @@ int fa_b200_last_status(int device, void* stream) {
     if (e != cudaSuccess) return static_cast<int>(e);
   }
   return static_cast<int>(words[0]);
+}
+
+// ------------------------------------------------------------------------- add + LayerNorm
+extern "C++" {
+namespace {
+
+template <int kVec>
+cudaError_t launch_add_ln(const fa::AddLnParams& kp, cudaStream_t stream) {
+  const long long ctas = (kp.rows + fa::kLnWarpsPerCta - 1) / fa::kLnWarpsPerCta;
+  fa::fa_add_layernorm_kernel<kVec><<<static_cast<unsigned>(ctas), fa::kLnWarpsPerCta * 32, 0, stream>>>(kp);
+  return cudaGetLastError();
+}
+
+}  // namespace
+}  // extern "C++"
+
+int fa_b200_add_layernorm(const fa_b200_add_layernorm_params* p) {
+  if (p == nullptr || p->a == nullptr || p->scale == nullptr || p->shift == nullptr ||
+      p->norm_out == nullptr)
+    return FA_B200_ERR_NULL;
+  if (p->rows < 0 || p->cols <= 0 || (p->cols % 8) != 0 ||
+      p->cols > fa::kLnMaxVecPerLane * 256)
+    return FA_B200_ERR_SHAPE;
+  if ((p->rows + fa::kLnWarpsPerCta - 1) / fa::kLnWarpsPerCta > 0x7fffffffLL) return FA_B200_ERR_SHAPE;
+  const void* ptrs[6] = {p->a, p->resid, p->scale, p->shift, p->sum_out, p->norm_out};
+  for (const void* q : ptrs)
+    if (reinterpret_cast<uintptr_t>(q) & 15u) return FA_B200_ERR_ALIGN;
+  if (!(p->eps >= 0.0f)) return FA_B200_ERR_SCALE;
+  if (p->device < 0 || p->device >= kMaxDevices) return FA_B200_ERR_DEVICE;
+  if (p->rows == 0) return FA_B200_OK;
+
+  DeviceGuard guard(p->device);
+  if (guard.error) return guard.error;
+  DeviceState& st = g_dev[p->device];
+  std::call_once(st.once, init_device, p->device);
+  if (st.init_error) return st.init_error;
+
+  fa::AddLnParams kp;
+  kp.a = static_cast<const __nv_bfloat16*>(p->a);
+  kp.resid = static_cast<const __nv_bfloat16*>(p->resid);
+  kp.scale = static_cast<const __nv_bfloat16*>(p->scale);
+  kp.shift = static_cast<const __nv_bfloat16*>(p->shift);
+  kp.sum_out = static_cast<__nv_bfloat16*>(p->sum_out);
+  kp.norm_out = static_cast<__nv_bfloat16*>(p->norm_out);
+  kp.rows = p->rows;
+  kp.cols = p->cols;
+  kp.eps = p->eps;
+  const cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+  cudaError_t e;
+  switch ((p->cols + 255) / 256) {   // 16-byte vectors per lane
+    case 1: e = launch_add_ln<1>(kp, stream); break;
+    case 2: e = launch_add_ln<2>(kp, stream); break;
+    case 3: e = launch_add_ln<3>(kp, stream); break;
+    case 4: e = launch_add_ln<4>(kp, stream); break;
+    case 5: e = launch_add_ln<5>(kp, stream); break;
+    case 6: e = launch_add_ln<6>(kp, stream); break;
+    case 7: e = launch_add_ln<7>(kp, stream); break;
+    default: e = launch_add_ln<8>(kp, stream); break;
+  }
+  return static_cast<int>(e);
 }
 
 #ifdef FA_TRACE

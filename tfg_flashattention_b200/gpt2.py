@@ -155,6 +155,12 @@ class FeedForward(nn.Module):
                                     nn.Linear(4 * config["emb_dim"], config["emb_dim"]))
 
     def forward(self, x):
+        fc, proj = self.layers[0], self.layers[2]
+        if x.is_cuda and x.dtype == torch.bfloat16 and not self.training and fc.weight.dtype == x.dtype:
+            # the tanh GELU runs in the epilogue of the first GEMM (cuBLASLt) instead of as a
+            # separate pass over the [tokens, 4*d_model] activation
+            h = torch._addmm_activation(fc.bias, x.reshape(-1, x.shape[-1]), fc.weight.t(), use_gelu=True)
+            return proj(h).view(*x.shape[:-1], proj.out_features)
         return self.layers(x)
 
 
@@ -195,6 +201,7 @@ class GPTModel(nn.Module):
         self.final_norm = LayerNorm(cfg)
         self.out_head = nn.Linear(cfg["emb_dim"], cfg["vocab_size"], bias=False)
         self._head_w = None     # out_head weight padded to a multiple of 64 rows (inference cache)
+        self._fused_blocks = False   # residual add + LayerNorm through block_ops.add_layernorm
         if dtype is not None:
             self.to(dtype)
 
@@ -207,6 +214,11 @@ class GPTModel(nn.Module):
         pad = (-w.shape[0]) % 64
         with torch.no_grad():
             self._head_w = F.pad(w, (0, 0, 0, pad)).contiguous() if pad else None
+        # bf16 model on a GPU with the attention kernel: every "x + branch; LayerNorm" pair of the
+        # blocks becomes one kernel of the library as well
+        d = self.cfg["emb_dim"]
+        self._fused_blocks = (w.is_cuda and w.dtype == torch.bfloat16 and self.cfg["impl_type"] == "cuda"
+                              and d % 8 == 0 and d <= 2048 and self.cfg["drop_rate"] == 0.0)
         return self
 
     def invalidate_inference_cache(self):
@@ -214,6 +226,7 @@ class GPTModel(nn.Module):
         for blk in self.trf_blocks:
             blk.att._qkv_w = blk.att._qkv_b = None
         self._head_w = None
+        self._fused_blocks = False
         return self
 
     def allocate_kv_cache(self, batch, max_len=None, dtype=None):
@@ -229,18 +242,68 @@ class GPTModel(nn.Module):
                  torch.zeros(batch, n_max, h, d, dtype=dtype, device=dev))
                 for _ in range(self.cfg["n_layers"])]
 
+    def _blocks_fused(self, x, kv_caches, pos, last_token_only):
+        """The block stack and the final norm with every shortcut addition folded into the
+        LayerNorm that follows it (TransformerBlock.forward computes the same values: x + att(
+        norm1(x)), then x + ff(norm2(x))).  `x` is the residual stream, updated in place; `branch`
+        is the output of the previous sub-layer that has not been added to it yet."""
+        from .block_ops import add_layernorm
+        branch = None
+        for i, blk in enumerate(self.trf_blocks):
+            cache = None if kv_caches is None else kv_caches[i]
+            if branch is None:
+                h = add_layernorm(x, None, blk.norm1.scale, blk.norm1.shift, blk.norm1.eps)
+            else:
+                x, h = add_layernorm(branch, x, blk.norm1.scale, blk.norm1.shift, blk.norm1.eps, sum_out=x)
+            branch = blk.att(h, cache, pos)
+            x, h = add_layernorm(branch, x, blk.norm2.scale, blk.norm2.shift, blk.norm2.eps, sum_out=x)
+            branch = blk.ff(h)
+        if last_token_only:               # what generate() consumes (model_inference.py:206)
+            x, branch = x[:, -1:, :].contiguous(), (None if branch is None else branch[:, -1:, :].contiguous())
+        fn = self.final_norm
+        return add_layernorm(x if branch is None else branch, None if branch is None else x,
+                             fn.scale, fn.shift, fn.eps, return_sum=False)
+
+    @torch.no_grad()
+    def capture_prefill(self, batch, n, last_token_only=False, warmup=3):
+        """Record one prefill forward for a fixed [batch, n] shape as a CUDA graph and return
+        `run(ids) -> logits`: the ~300 launches of a forward (GEMMs, attention, add+LayerNorm) are
+        replayed as one graph launch, which removes the host gaps between them.  The returned
+        logits live in the graph's own memory and are overwritten by the next call."""
+        dev = self.tok_emb.weight.device
+        static_ids = torch.zeros(batch, n, dtype=torch.long, device=dev)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):          # first calls set up library state: keep them out of the capture
+            for _ in range(warmup):
+                self(static_ids, last_token_only=last_token_only)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            static_out = self(static_ids, last_token_only=last_token_only)
+
+        def run(ids):
+            static_ids.copy_(ids)
+            graph.replay()
+            return static_out
+        run.graph = graph
+        return run
+
     def forward(self, in_idx, last_token_only=False, kv_caches=None, pos=0):
         _, n = in_idx.shape
         x = self.tok_emb(in_idx) + self.pos_emb(torch.arange(pos, pos + n, device=in_idx.device))
         x = self.drop_emb(x)
-        if kv_caches is None:
-            x = self.trf_blocks(x)
+        if self._fused_blocks and not self.training and x.dtype == torch.bfloat16:
+            x = self._blocks_fused(x.contiguous(), kv_caches, pos, last_token_only)
         else:
-            for blk, cache in zip(self.trf_blocks, kv_caches):
-                x = blk(x, cache, pos)
-        x = self.final_norm(x)
-        if last_token_only:           # what generate() consumes (model_inference.py:206)
-            x = x[:, -1:, :]
+            if kv_caches is None:
+                x = self.trf_blocks(x)
+            else:
+                for blk, cache in zip(self.trf_blocks, kv_caches):
+                    x = blk(x, cache, pos)
+            x = self.final_norm(x)
+            if last_token_only:           # what generate() consumes (model_inference.py:206)
+                x = x[:, -1:, :]
         if self._head_w is not None and not self.training:
             return F.linear(x, self._head_w)[..., :self.out_head.weight.shape[0]]
         return self.out_head(x)
