@@ -203,6 +203,36 @@ def time_e2e(cfa, w, rank, steps, warmup, world):
     return ms, 3 * nbytes, nbytes
 
 
+def time_add_layernorm(rows, cols, steps, warmup):
+    """s = a + resid (written in place over resid), y = LayerNorm(s): 4 * rows * cols * 2 algorithmic
+    bytes per launch.  Buffer sets are rotated so that no launch finds its inputs in L2."""
+    from tfg_flashattention_b200.block_ops import add_layernorm
+    g = torch.Generator(device="cuda").manual_seed(13)
+    one_set = 3 * rows * cols * 2
+    n_sets = max(2, min(8, int(400e6 // one_set) + 1))
+    sets = [(torch.randn(rows, cols, device="cuda", generator=g).bfloat16(),
+             torch.randn(rows, cols, device="cuda", generator=g).bfloat16(),
+             torch.empty(rows, cols, device="cuda", dtype=torch.bfloat16)) for _ in range(n_sets)]
+    scale = torch.ones(cols, device="cuda", dtype=torch.bfloat16)
+    shift = torch.zeros(cols, device="cuda", dtype=torch.bfloat16)
+    def step(i):
+        a, x, y = sets[i % n_sets]
+        add_layernorm(a, x, scale, shift, 1e-5, sum_out=x, norm_out=y)
+    for i in range(warmup):
+        step(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    return {"rows": rows, "cols": cols, "us_per_launch": round(ms * 1e3, 2),
+            "gbs": round(4.0 * rows * cols * 2 / (ms * 1e-3) / 1e9, 1), "buffer_sets_rotated": n_sets,
+            "kernel": "fa::fa_add_layernorm_kernel"}
+
+
 def cpu_attention_sample(w, reps, threads):
     """Time the CPU oracle on CPU_SAMPLE_BATCH batch entries of workload w.  Returns TFLOP/s."""
     from oracle.attention_oracle import manual_attention
@@ -274,6 +304,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--decode-case", default=None, metavar="B,H,kv_len",
                     help="time only this decode step (small runs for profilers); prints a short line")
+    ap.add_argument("--ln-case", default=None, metavar="rows,cols",
+                    help="time only the residual add + LayerNorm kernel on this shape (for profiling)")
     ap.add_argument("--case", default=None, metavar="B,H,N,causal",
                     help="time only this attention problem (small runs for profilers); prints a short line")
     args = ap.parse_args()
@@ -312,6 +344,11 @@ def main():
         print(json.dumps({"decode_case": args.decode_case, "us_per_step": dms * 1e3,
                           "gbs": 2.0 * db * dh * dn * 128 / (dms * 1e-3) / 1e9,
                           "status": cfa.last_status()}), flush=True)
+        return
+
+    if args.ln_case:
+        lr, lc = (int(x) for x in args.ln_case.split(","))
+        print(json.dumps({"ln_case": args.ln_case, **time_add_layernorm(lr, lc, args.steps, args.warmup)}), flush=True)
         return
 
     if args.case:
@@ -455,6 +492,14 @@ def main():
         if cfa.last_status() != 0:
             raise SystemExit("kernel watchdog fired during the decode runs")
 
+    # ---------------------------------------------------------------- residual add + LayerNorm kernel
+    add_ln = []
+    if not args.no_sweep:
+        for rows, cols in ((32 * 1024, 1600), (8 * 1024, 768)):      # GPT-2 XL B=32 and small B=8 prefill
+            r = time_add_layernorm(rows, cols, 40, 5)
+            r["frac_of_hbm_peak"] = round(r["gbs"] / peaks["hbm_gbs"], 3)
+            add_ln.append(r)
+
     # ---------------------------------------------------------------- the reference's own benchmark
     # "time for 20 tokens" (model_inference.py:444-465): B=1, a ~70-token prompt, 20 new tokens,
     # here with random-init weights and random token ids; with the K/V cache + decode kernel, and
@@ -516,7 +561,7 @@ def main():
             "gpu_launches": args.steps,
             "clocks": clocks,
             "cpu_baseline": cpu,
-            "extra": {"sweep": sweep, "gpt2_prefill": prefill, "decode_step": decode,
+            "extra": {"sweep": sweep, "gpt2_prefill": prefill, "decode_step": decode, "add_layernorm": add_ln,
                       "generate_20_tokens": gen},
         }
         print(json.dumps(line), flush=True)
