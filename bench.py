@@ -513,20 +513,23 @@ def main():
             model.prepare_for_inference()
             prompt = torch.randint(0, cfg["vocab_size"], (gb, gp), generator=torch.Generator().manual_seed(123)).cuda()
             row = {"model": name, "prompt_tokens": gp, "new_tokens": 20, "batch": gb, "dtype": "bf16",
-                   "note": "B=1 with a short prompt is launch-bound (Python + ~15 launches per layer and token); "
-                           "the cache pays with longer prompts and batches"}
-            for label, use_cache in (("kv_cache_ms", True), ("recompute_ms", False)):
-                gpt2.generate(model, prompt, 20, 1024, temperature=0.0, use_cache=use_cache)
+                   "note": "eager B=1 steps are launch-bound (Python + ~15 launches per layer and token); "
+                           "kv_cache_graph_ms replays one recorded CUDA graph per token (prefill eager)"}
+            session = gpt2.GenerationSession(model, gb, 1024)      # caches + recorded decode step, reused
+            for label, kw in (("kv_cache_graph_ms", {"session": session}), ("kv_cache_ms", {}),
+                              ("recompute_ms", {"use_cache": False})):
+                gpt2.generate(model, prompt, 20, 1024, temperature=0.0, **kw)
                 torch.cuda.synchronize()
                 times = []
                 for _ in range(3):
                     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                     e0.record()
-                    gpt2.generate(model, prompt, 20, 1024, temperature=0.0, use_cache=use_cache)
+                    gpt2.generate(model, prompt, 20, 1024, temperature=0.0, **kw)
                     e1.record()
                     torch.cuda.synchronize()
                     times.append(e0.elapsed_time(e1))
                 row[label] = round(statistics.median(times), 2)
+            del session
             gen.append(row)
             del model
             torch.cuda.empty_cache()

@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define FA_B200_ABI_VERSION 1
+#define FA_B200_ABI_VERSION 2
 
 /* argument errors (negative return values) */
 #define FA_B200_OK                 0
@@ -130,6 +130,12 @@ typedef struct fa_b200_decode_params {
   float       softmax_scale;  /* 0 selects 1/sqrt(d) */
   int32_t     device;
   void*       stream;
+  /* Optional (ABI version 2).  When not NULL: device address of an int32 that holds the current
+   * number of valid cache rows; the kernel reads it when it RUNS, so one recorded launch (a CUDA
+   * graph node) serves every step of a generation loop while the host only bumps that counter on
+   * the device.  kv_len is then the upper bound the launch is sized for (grid, workspace); the
+   * value read is clamped to [1, kv_len]. */
+  const int32_t* kv_len_device;
 } fa_b200_decode_params;
 
 /* Bytes of workspace fa_b200_decode needs for this problem size (0 when the keys of a head are

@@ -142,3 +142,57 @@ def test_bf16_model_prefill_small(fa_lib):
         b = m(ids).float()
     assert torch.isfinite(a).all()
     assert (a - b).abs().max().item() < 5e-2
+
+
+@pytest.mark.gpu
+def test_decode_with_length_on_the_device(fa_lib):
+    """kv_len as an int32 on the GPU: the launch is sized for the whole cache, the kernel reads the
+    length when it runs; every length gives exactly what the host-side length gives."""
+    from tfg_flashattention_b200 import custom_flash_attn as cfa
+    torch.manual_seed(3)
+    for B, H, cap in ((2, 3, 300), (32, 25, 128), (1, 1, 1000)):
+        q = torch.randn(B, H, 64, device="cuda").bfloat16()
+        k = torch.randn(B, H, cap, 64, device="cuda").bfloat16()
+        v = torch.randn(B, H, cap, 64, device="cuda").bfloat16()
+        length = torch.ones(1, dtype=torch.int32, device="cuda")
+        for n in (1, 2, 63, 64, 65, cap // 2, cap - 1, cap):
+            length.fill_(n)
+            o_dev, lse_dev = cfa.decode(q, k, v, length, return_lse=True)
+            o_host, lse_host = cfa.decode(q, k, v, n, return_lse=True)
+            # the chunking differs (sized for `cap` instead of `n`): equal up to fp32 summation order
+            torch.testing.assert_close(o_dev.float(), o_host.float(), rtol=0, atol=2e-2)
+            torch.testing.assert_close(lse_dev, lse_host, rtol=1e-5, atol=1e-5)
+        length.fill_(cap + 50)                      # clamped to the cache size
+        torch.testing.assert_close(cfa.decode(q, k, v, length).float(), cfa.decode(q, k, v, cap).float(),
+                                   rtol=0, atol=2e-2)
+    assert cfa.last_status() == 0
+    with pytest.raises(RuntimeError):
+        cfa.decode(q, k, v, torch.ones(1, dtype=torch.int64, device="cuda"))
+
+
+@pytest.mark.gpu
+def test_generation_with_graph_replay_equals_eager_cache_path(golden_dir, fa_lib):
+    """generate(cuda_graph=True): the single-token forward recorded once and replayed per token
+    picks the same greedy tokens as the eager K/V-cache loop, on the fp32 and the bf16 model."""
+    model, ids, _ = _load_tiny(golden_dir, "cuda")
+    model = model.cuda()
+    ids = ids.cuda()
+    a = gpt2.generate(model, ids[:, :12], 10, 48, temperature=0.0)
+    b = gpt2.generate(model, ids[:, :12], 10, 48, temperature=0.0, cuda_graph=True)
+    assert torch.equal(a, b)
+    cfg = {"vocab_size": 503, "context_length": 128, "emb_dim": 256, "n_heads": 4, "n_layers": 3,
+           "drop_rate": 0.0, "qkv_bias": True, "impl_type": "cuda"}
+    m = gpt2.init_random(gpt2.GPTModel(cfg, dtype=torch.bfloat16), seed=9, std=0.05).cuda().eval()
+    m.prepare_for_inference()
+    prompt = torch.randint(0, 503, (3, 40), device="cuda")
+    a = gpt2.generate(m, prompt, 20, 128, temperature=0.0)
+    b = gpt2.generate(m, prompt, 20, 128, temperature=0.0, cuda_graph=True)
+    assert a.shape == b.shape == (3, 60)
+    assert torch.equal(a, b)
+    session = gpt2.GenerationSession(m, 3, 128)                 # recorded once, used for two prompts
+    assert torch.equal(gpt2.generate(m, prompt, 20, 128, temperature=0.0, session=session), a)
+    prompt2 = torch.randint(0, 503, (3, 17), device="cuda")
+    assert torch.equal(gpt2.generate(m, prompt2, 9, 128, temperature=0.0, session=session),
+                       gpt2.generate(m, prompt2, 9, 128, temperature=0.0))
+    from tfg_flashattention_b200 import custom_flash_attn
+    assert custom_flash_attn.last_status() == 0

@@ -10,7 +10,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libfa_b200.so")
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 
 class FaParams(ctypes.Structure):
@@ -36,6 +36,7 @@ class FaDecodeParams(ctypes.Structure):
         ("q_strides", ctypes.c_int64 * 2), ("o_strides", ctypes.c_int64 * 2),
         ("k_strides", ctypes.c_int64 * 3), ("v_strides", ctypes.c_int64 * 3),
         ("softmax_scale", ctypes.c_float), ("device", ctypes.c_int32), ("stream", ctypes.c_void_p),
+        ("kv_len_device", ctypes.c_void_p),
     ]
 
 

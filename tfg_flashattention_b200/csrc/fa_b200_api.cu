@@ -269,6 +269,7 @@ int decode_validate(const fa_b200_decode_params* p) {
   for (uintptr_t a : ptrs)
     if (a & 15u) return FA_B200_ERR_ALIGN;
   if (p->lse != nullptr && (reinterpret_cast<uintptr_t>(p->lse) & 3u)) return FA_B200_ERR_ALIGN;
+  if (p->kv_len_device != nullptr && (reinterpret_cast<uintptr_t>(p->kv_len_device) & 3u)) return FA_B200_ERR_ALIGN;
   if (!(p->softmax_scale >= 0.0f) || std::isinf(p->softmax_scale)) return FA_B200_ERR_SCALE;
   if (p->device < 0 || p->device >= kMaxDevices) return FA_B200_ERR_DEVICE;
   return FA_B200_OK;
@@ -315,6 +316,7 @@ int fa_b200_decode(const fa_b200_decode_params* p) {
   kp.k_sb = p->k_strides[0]; kp.k_sh = p->k_strides[1]; kp.k_sn = p->k_strides[2];
   kp.v_sb = p->v_strides[0]; kp.v_sh = p->v_strides[1]; kp.v_sn = p->v_strides[2];
   kp.B = p->B; kp.H = p->H; kp.kv_len = p->kv_len;
+  kp.kv_len_ptr = p->kv_len_device;
   kp.splits = splits;
   kp.rows_per_split = rows;
   const float scale = p->softmax_scale > 0.0f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(p->d));
@@ -389,6 +391,7 @@ int fa_b200_decode_static(const fa_b200_decode_params* p) {
   kp.k_sb = p->k_strides[0]; kp.k_sh = p->k_strides[1]; kp.k_sn = p->k_strides[2];
   kp.v_sb = p->v_strides[0]; kp.v_sh = p->v_strides[1]; kp.v_sn = p->v_strides[2];
   kp.B = p->B; kp.H = p->H; kp.kv_len = p->kv_len;
+  kp.kv_len_ptr = p->kv_len_device;
   kp.splits = splits;
   kp.rows_per_split = rows;
   const float scale = p->softmax_scale > 0.0f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(p->d));

@@ -46,6 +46,9 @@ struct DecodeParams {
   int splits;                  // chunks per head
   int rows_per_split;          // multiple of kDecodeGroups
   float scale_log2;            // softmax_scale * log2(e)
+  const int* kv_len_ptr = nullptr;   // when set: the current length lives in device memory (read
+                                     // at run time, clamped to [1, kv_len]); kv_len is the bound
+                                     // the grid and the chunks were sized for
 };
 
 __device__ __forceinline__ void bf16x8_to_float(const uint4& raw, float (&f)[8]) {
@@ -78,8 +81,9 @@ __global__ void __launch_bounds__(kDecodeThreads) fa_decode_partial_kernel(const
   }
   const __nv_bfloat16* kbase = p.k + b * p.k_sb + h * p.k_sh + 8 * c;
   const __nv_bfloat16* vbase = p.v + b * p.v_sb + h * p.v_sh + 8 * c;
+  const int kv_len = p.kv_len_ptr ? max(1, min(__ldg(p.kv_len_ptr), p.kv_len)) : p.kv_len;
   const int row_begin = split * p.rows_per_split;
-  const int row_end = min(p.kv_len, row_begin + p.rows_per_split);
+  const int row_end = min(kv_len, row_begin + p.rows_per_split);   // chunks past the end stay empty
 
   float m = -CUDART_INF_F, l = 0.f;
   float acc[8];

@@ -111,7 +111,8 @@ def decode(Q, K_cache, V_cache, kv_len, return_lse=False, softmax_scale=None, ou
     counterpart -- its generate() recomputes the whole prefix, model_inference.py:199-228).
 
     Q [B, H, 64] (or [B, H, 1, 64]) bf16; K_cache, V_cache [B, H, >= kv_len, 64] bf16 (any row /
-    head / batch strides that are multiples of 8 elements); attends rows 0 .. kv_len-1.
+    head / batch strides that are multiples of 8 elements); attends rows 0 .. kv_len-1.  kv_len is
+    an int, or a one-element int32 CUDA tensor that is read by the kernel when it runs.
     Returns O shaped like Q (and LSE [B, H] fp32 when asked).  The split-KV workspace is a cached
     torch buffer per device; calls on one stream may share it, calls that overlap on different
     streams of one device must not (pass through separate processes or serialise them)."""
@@ -129,6 +130,14 @@ def decode(Q, K_cache, V_cache, kv_len, return_lse=False, softmax_scale=None, ou
     B, H, d = q3.shape
     if K_cache.shape[:2] != (B, H) or V_cache.shape != K_cache.shape or K_cache.shape[3] != d:
         raise RuntimeError("Q, K_cache and V_cache disagree on B, H or d")
+    kv_len_dev = None
+    if isinstance(kv_len, torch.Tensor):
+        # the length lives on the device (an int32 scalar that the caller advances between steps):
+        # the launch is sized for the whole cache and the kernel reads the length when it runs,
+        # which is what lets one recorded CUDA-graph launch serve every step of a generation loop
+        if not (kv_len.is_cuda and kv_len.dtype == torch.int32 and kv_len.numel() == 1):
+            raise RuntimeError("a tensor kv_len must be one int32 on the GPU")
+        kv_len_dev, kv_len = kv_len, K_cache.shape[2]
     kv_len = int(kv_len)
     if not 1 <= kv_len <= K_cache.shape[2]:
         raise RuntimeError("kv_len must be between 1 and the cache length")
@@ -189,6 +198,7 @@ def decode(Q, K_cache, V_cache, kv_len, return_lse=False, softmax_scale=None, ou
     p.softmax_scale = 0.0 if softmax_scale is None else float(softmax_scale)
     p.device = Q.device.index if Q.device.index is not None else torch.cuda.current_device()
     p.stream = torch.cuda.current_stream(Q.device).cuda_stream
+    p.kv_len_device = kv_len_dev.data_ptr() if kv_len_dev is not None else None
     rc = lib.fa_b200_decode(ctypes.byref(p))
     if rc != 0:
         raise RuntimeError(f"custom_flash_attn.decode failed ({rc}): {_lib.strerror(rc)}")

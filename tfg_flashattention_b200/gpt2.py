@@ -61,6 +61,24 @@ def gpt2_config(name: str, impl_type: str = "cuda", context_length: int = 1024) 
     return cfg
 
 
+class DevicePosition:
+    """Where the next token goes, kept on the GPU so that a recorded decode step needs no host
+    value: `index` (int64 [1]) addresses the cache row and the position embedding, `length`
+    (int32 [1]) = index + 1 is what the decode kernel reads as the number of valid rows."""
+
+    def __init__(self, device):
+        self.index = torch.zeros(1, dtype=torch.long, device=device)
+        self.length = torch.ones(1, dtype=torch.int32, device=device)
+
+    def set(self, pos: int):
+        self.index.fill_(pos)
+        self.length.fill_(pos + 1)
+
+    def advance(self):
+        self.index.add_(1)
+        self.length.add_(1)
+
+
 class MultiHeadAttention(nn.Module):
     def __init__(self, d_in, d_out, context_length, dropout, num_heads, impl_type, qkv_bias=False):
         super().__init__()
@@ -98,16 +116,24 @@ class MultiHeadAttention(nn.Module):
             q = self.W_query(x).view(b, n, h, d).transpose(1, 2)
             k = self.W_key(x).view(b, n, h, d).transpose(1, 2)
             v = self.W_value(x).view(b, n, h, d).transpose(1, 2)
+        dev_pos = isinstance(pos, DevicePosition)   # decode step inside a CUDA graph
+        if dev_pos and not (self.impl_type == "cuda" and n == 1 and kv_cache is not None):
+            raise NotImplementedError("a device-side position is for single-token steps of the cuda path")
         if kv_cache is not None:
             ck, cv = kv_cache
-            ck[:, pos:pos + n] = k.transpose(1, 2).to(ck.dtype)
-            cv[:, pos:pos + n] = v.transpose(1, 2).to(cv.dtype)
+            if dev_pos:
+                ck.index_copy_(1, pos.index, k.transpose(1, 2).to(ck.dtype))
+                cv.index_copy_(1, pos.index, v.transpose(1, 2).to(cv.dtype))
+            else:
+                ck[:, pos:pos + n] = k.transpose(1, 2).to(ck.dtype)
+                cv[:, pos:pos + n] = v.transpose(1, 2).to(cv.dtype)
         if self.impl_type == "cuda":
             from . import custom_flash_attn
             if q.dtype != torch.bfloat16:      # outside autocast: the kernel is bf16-only
                 q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
             if kv_cache is not None and n == 1:
-                ctx = custom_flash_attn.decode(q, ck.transpose(1, 2), cv.transpose(1, 2), pos + 1)
+                ctx = custom_flash_attn.decode(q, ck.transpose(1, 2), cv.transpose(1, 2),
+                                               pos.length if dev_pos else pos + 1)
                 ctx = ctx.transpose(1, 2)                                    # [B, 1, H, d]
             elif pos == 0:
                 ctx = custom_flash_attn.forward(q, k, v).transpose(1, 2)     # [B,N,H,d], dense
@@ -289,9 +315,42 @@ class GPTModel(nn.Module):
         run.graph = graph
         return run
 
+    @torch.no_grad()
+    def capture_decode_step(self, kv_caches, warmup=2):
+        """Record one generation step (one new token per sequence against `kv_caches`) as a CUDA
+        graph.  Returns `step(ids [B,1]) -> logits [B,1,vocab]` and the DevicePosition it advances:
+        call `position.set(prompt_len)` after the prefill has filled the caches, then `step` once
+        per token.  A step is then one graph launch instead of ~15 kernel launches per layer, which
+        is what bounds small-batch generation.  The warm-up steps write cache row 0 and are
+        overwritten by the prefill, so capture BEFORE running the prompt."""
+        dev = self.tok_emb.weight.device
+        batch = kv_caches[0][0].shape[0]
+        position = DevicePosition(dev)
+        static_ids = torch.zeros(batch, 1, dtype=torch.long, device=dev)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(warmup):
+                self(static_ids, kv_caches=kv_caches, pos=position)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            static_logits = self(static_ids, kv_caches=kv_caches, pos=position)
+            position.advance()
+
+        def step(ids):
+            static_ids.copy_(ids)
+            graph.replay()
+            return static_logits
+        step.graph = graph
+        return step, position
+
     def forward(self, in_idx, last_token_only=False, kv_caches=None, pos=0):
         _, n = in_idx.shape
-        x = self.tok_emb(in_idx) + self.pos_emb(torch.arange(pos, pos + n, device=in_idx.device))
+        if isinstance(pos, DevicePosition):
+            x = self.tok_emb(in_idx) + self.pos_emb(pos.index)
+        else:
+            x = self.tok_emb(in_idx) + self.pos_emb(torch.arange(pos, pos + n, device=in_idx.device))
         x = self.drop_emb(x)
         if self._fused_blocks and not self.training and x.dtype == torch.bfloat16:
             x = self._blocks_fused(x.contiguous(), kv_caches, pos, last_token_only)
@@ -309,24 +368,53 @@ class GPTModel(nn.Module):
         return self.out_head(x)
 
 
+class GenerationSession:
+    """K/V caches for `batch` sequences of up to `context_size` tokens plus (cuda_graph=True) the
+    recorded single-token step; pass it to generate() to reuse both across prompts."""
+
+    @torch.no_grad()
+    def __init__(self, model, batch, context_size, cuda_graph=True):
+        self.batch, self.context_size = batch, context_size
+        self.caches = model.allocate_kv_cache(batch, context_size)
+        self.step_fn = self.position = None
+        if cuda_graph:
+            self.step_fn, self.position = model.capture_decode_step(self.caches)
+
+
 @torch.no_grad()
 def generate(model, idx, max_new_tokens, context_size, temperature=1.0, top_k=None, eos_id=None,
-             use_cache=True, generator=None):
+             use_cache=True, generator=None, cuda_graph=False, session=None):
     """The reference's generate() (model_inference.py:199-228): same arguments, same top-k /
     temperature / multinomial-or-argmax rules, same stop at eos_id.  With use_cache=True the
     prompt is run once and each new token costs one single-token forward against the K/V cache;
-    with use_cache=False every token re-runs `idx[:, -context_size:]` as the reference does."""
+    with use_cache=False every token re-runs `idx[:, -context_size:]` as the reference does.
+    cuda_graph=True (with the cache, "cuda" attention) records the single-token forward once and
+    replays it per token: one graph launch instead of ~15 kernel launches per layer.  Recording
+    costs a few steps' time; `session=GenerationSession(model, batch, context_size)` keeps the
+    caches and the recorded step across calls."""
     caches = None
     pos = 0
+    step_fn = position = None
     if use_cache:
         if idx.shape[1] + max_new_tokens > context_size:
             raise ValueError("prompt + new tokens exceed the context length (the cache does not slide)")
-        caches = model.allocate_kv_cache(idx.shape[0], context_size)
+        if session is not None:            # caches and the recorded step are reused across calls
+            if session.batch != idx.shape[0] or session.context_size < idx.shape[1] + max_new_tokens:
+                raise ValueError("the generation session was made for another batch or context size")
+            caches, step_fn, position = session.caches, session.step_fn, session.position
+        else:
+            caches = model.allocate_kv_cache(idx.shape[0], context_size)
+            if cuda_graph:
+                step_fn, position = model.capture_decode_step(caches)
     for step in range(max_new_tokens):
-        if use_cache:
+        if use_cache and step > 0 and step_fn is not None:
+            logits = step_fn(idx[:, -1:])
+        elif use_cache:
             inp = idx if step == 0 else idx[:, -1:]
             logits = model(inp, last_token_only=True, kv_caches=caches, pos=pos)
             pos += inp.shape[1]
+            if position is not None:
+                position.set(pos)
         else:
             logits = model(idx[:, -context_size:], last_token_only=True)
         logits = logits[:, -1, :].float()
