@@ -42,9 +42,9 @@ from tfg_flashattention_b200 import workloads  # noqa: E402
 METRIC = "causal_attention_fwd_tflops"
 UNIT = "TFLOP/s"
 # DRAM bytes per launch of fa_fwd_kernel on the headline workload (dram__bytes_read.sum +
-# dram__bytes_write.sum).  Captured with ncu at B=12 (118.04 + 20.30 MB per launch) and scaled by
+# dram__bytes_write.sum).  Captured with ncu at B=12 (118.03 + 18.10 MB per launch) and scaled by
 # 32/12 to the benchmark's B=32: every (batch, head) is independent, so traffic grows in proportion.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 138.34e6 * 32 / 12
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 136.13e6 * 32 / 12
 E2E_CHUNKS = 8                # batch slices the host-buffer call pipelines through PCIe
 CPU_SAMPLE_BATCH = 4          # batch entries (x25 heads) the CPU legs compute per repetition
 
@@ -558,7 +558,7 @@ def main():
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["bf16_tflops"],
                          "unit": "TFLOP/s", "frac": per_gpu / peaks["bf16_tflops"],
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": f"of {peaks['source']}",
-                         "algorithmic_bytes": w.bytes(), "kernel": "fa::fa_fwd_kernel<true> (persistent instantiation)"},
+                         "algorithmic_bytes": w.bytes(), "kernel": "fa::fa_fwd_kernel<true, true> (persistent, causal instantiation)"},
             "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": args.steps,
