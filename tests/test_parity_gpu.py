@@ -187,6 +187,36 @@ def test_long_context_stress_rows(cfa):
 
 
 @pytest.mark.parametrize("causal", [True, False])
+def test_one_hot_rows_far_below_the_exponent_clamp(cfa, causal):
+    """Scores 30*j (43 per key in exp2 units): every key but the winner sits more than 126 below
+    the row maximum from the third neighbour on, i.e. in the range where the FMA-pipe exp2 clamps
+    its argument and the MUFU one flushes to zero.  Both must produce (almost) zeros, never
+    garbage exponents: the output row is the winner's V row, the LSE is the winning score."""
+    N = 384
+    q = torch.zeros(1, 1, N, 64)
+    k = torch.zeros(1, 1, N, 64)
+    q[..., 0] = 240.0                                   # exact in bf16; scale 1/8 -> 30 per key index
+    k[..., 0] = (torch.arange(N) % 256).float()         # integers up to 255 are exact in bf16
+    v = torch.randn(1, 1, N, 64, generator=torch.Generator().manual_seed(5))
+    qb, kb, vb = (t.to("cuda", torch.bfloat16) for t in (q, k, v))
+    o, lse = cfa.forward(qb, kb, vb, causal=causal, return_lse=True)
+    assert cfa.last_status() == 0
+    assert torch.isfinite(o).all() and torch.isfinite(lse).all()
+    ro, rl = _oracle().manual_attention(qb.float().cpu(), kb.float().cpu(), vb.float().cpu(),
+                                        causal=causal, return_lse=True)
+    assert (o.float().cpu() - ro).abs().max().item() <= MAX_ABS
+    assert ((lse.cpu() - rl).abs() <= 1e-3 * rl.abs().clamp_min(1.0)).all()
+    # the winner: key index 255 of the visible prefix's best residue class
+    scores = 30.0 * (torch.arange(N) % 256).float()
+    for row in (0, 1, 2, 130, 255, 256, 300, N - 1):
+        visible = scores[: row + 1] if causal else scores
+        best = visible.max()
+        winners = (visible == best).nonzero().flatten()
+        want = vb.float().cpu()[0, 0, winners].mean(0)
+        assert (o.float().cpu()[0, 0, row] - want).abs().max().item() <= MAX_ABS
+
+
+@pytest.mark.parametrize("causal", [True, False])
 def test_extreme_score_jumps(cfa, causal):
     """Key rows scaled x64 push some scores ~2^90 (in exp2 units) above everything seen before
     them: the running-max rescale of O and l must keep the result finite and equal to the oracle.
