@@ -204,6 +204,31 @@ typedef struct fa_b200_add_layernorm_params {
 
 int fa_b200_add_layernorm(const fa_b200_add_layernorm_params* p);
 
+/* y = act(x W^T + bias) for at most 8 rows of x (the Linear layers of a generation step):
+ * x [M, K], W [N, K] with row stride ldw (elements; the layout of torch.nn.Linear.weight), bias
+ * [N] or NULL, y [M, N]; all bf16, fp32 accumulation; act 0 = none, 1 = tanh-GELU.
+ *
+ * Replaces, for single-token steps, the nn.Linear calls of the reference's attention module
+ * (src/py/model_inference.py:50-53, 93), feed-forward (:121-125 with the GELU of :109-117) and
+ * output head (:190).  HBM-bound on reading W once.  1 <= M <= 8; K a positive multiple of 8 with
+ * M_padded * K * 2 bytes <= 128 KiB (M_padded = M rounded up to 1, 2, 4 or 8); ldw >= K, a
+ * multiple of 8; x, W, y 16-byte aligned, bias 2-byte aligned.  N == 0 is a no-op.  Asynchronous on
+ * p->stream.  Errors: FA_B200_ERR_NULL, _SHAPE, _STRIDE, _ALIGN, _DEVICE, _ARCH or a positive
+ * cudaError_t. */
+typedef struct fa_b200_linear_small_params {
+  const void* x;
+  const void* w;
+  const void* bias;       /* or NULL */
+  void* y;
+  int32_t M, N, K;
+  int64_t ldw;
+  int32_t act;
+  int32_t device;
+  void* stream;
+} fa_b200_linear_small_params;
+
+int fa_b200_linear_small(const fa_b200_linear_small_params* p);
+
 /* FA_B200_ABI_VERSION the library was built with. */
 int fa_b200_abi_version(void);
 

@@ -138,3 +138,24 @@ def test_add_layernorm_rejects_before_any_cuda_call(fa_lib):
     assert call(params(eps=-1.0)) == -6
     assert call(params(device=-2)) == -7
     assert call(params(rows=0)) == 0               # nothing to do, nothing launched
+
+
+def test_linear_small_rejects_before_any_cuda_call(fa_lib):
+    def params(**kw):
+        p = _lib.FaLinearSmallParams()
+        p.x, p.w, p.bias, p.y = 0x1000, 0x2000, 0x3000, 0x4000
+        p.M, p.N, p.K, p.ldw, p.act, p.device, p.stream = 1, 4800, 1600, 1600, 0, 0, None
+        for k, v in kw.items():
+            setattr(p, k, v)
+        return p
+    call = lambda p: fa_lib.fa_b200_linear_small(ctypes.byref(p))
+    assert fa_lib.fa_b200_linear_small(None) == -1
+    assert call(params(w=None)) == -1
+    assert call(params(M=0)) == -3 and call(params(M=9)) == -3
+    assert call(params(K=1604)) == -3
+    assert call(params(M=8, K=8200, ldw=8200)) == -3     # 8 rows x 8200 x 2 bytes > 128 KiB
+    assert call(params(act=2)) == -3
+    assert call(params(ldw=1592)) == -4
+    assert call(params(x=0x1008)) == -5
+    assert call(params(device=-1)) == -7
+    assert call(params(N=0)) == 0

@@ -86,3 +86,41 @@ def test_fused_block_path_equals_module_by_module_path(fa_lib):
     assert (fused - plain).abs().max().item() <= 0.03 * scale      # bf16 rounding at different places
     assert (fused - plain).abs().mean().item() <= 0.004 * scale
     torch.testing.assert_close(last, fused[:, -1:, :], rtol=0, atol=0.02 * scale)
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 5, 8])
+@pytest.mark.parametrize("N,K", [(7, 8), (64, 64), (4800, 1600), (1600, 6400), (50257, 768)])
+def test_linear_small_matches_fp32(fa_lib, M, N, K):
+    """y = act(x W^T + b) for a few rows: against the fp32 product of the same bf16 numbers."""
+    from tfg_flashattention_b200.block_ops import linear_small
+    g = torch.Generator(device="cuda").manual_seed(M * 100003 + N + K)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    b = torch.randn(N, device="cuda", generator=g).bfloat16()
+    ref = x.float() @ w.float().t()
+    for bias, gelu in ((None, False), (b, False), (b, True)):
+        want = ref + (bias.float() if bias is not None else 0.0)
+        if gelu:
+            want = torch.nn.functional.gelu(want, approximate="tanh")
+        got = linear_small(x, w, bias, gelu=gelu).float()
+        assert got.shape == (M, N)
+        # fp32 accumulation, one rounding to bf16
+        assert ((got - want).abs() <= 2.0 ** -8 * want.abs() + 1e-3).all(), (got - want).abs().max().item()
+
+
+def test_linear_small_strided_weight_3d_input_and_errors(fa_lib):
+    from tfg_flashattention_b200.block_ops import linear_small
+    torch.manual_seed(1)
+    big = torch.randn(300, 512, device="cuda").bfloat16()
+    w = big[:, 128:384]                                   # rows 512 apart, 256 columns used
+    x = torch.randn(2, 1, 256, device="cuda").bfloat16()   # [B, 1, K] as in a decode step
+    got = linear_small(x, w).float()
+    assert got.shape == (2, 1, 300)
+    want = x.float().view(2, 256) @ w.float().t()
+    assert ((got.view(2, 300) - want).abs() <= 2.0 ** -8 * want.abs() + 1e-3).all()
+    with pytest.raises(RuntimeError, match="fa_b200"):
+        linear_small(torch.zeros(9, 64, device="cuda").bfloat16(), torch.zeros(8, 64, device="cuda").bfloat16())
+    with pytest.raises(RuntimeError):
+        linear_small(torch.zeros(2, 60, device="cuda").bfloat16(), torch.zeros(8, 60, device="cuda").bfloat16())
+    with pytest.raises(RuntimeError):
+        linear_small(x, w.float())

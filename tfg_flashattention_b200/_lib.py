@@ -50,9 +50,18 @@ class FaAddLnParams(ctypes.Structure):
     ]
 
 
+class FaLinearSmallParams(ctypes.Structure):
+    """struct fa_b200_linear_small_params (include/fa_b200.h)."""
+    _fields_ = [
+        ("x", ctypes.c_void_p), ("w", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("y", ctypes.c_void_p),
+        ("M", ctypes.c_int32), ("N", ctypes.c_int32), ("K", ctypes.c_int32), ("ldw", ctypes.c_int64),
+        ("act", ctypes.c_int32), ("device", ctypes.c_int32), ("stream", ctypes.c_void_p),
+    ]
+
+
 EXPORTS = ("fa_b200_fwd", "fa_b200_validate", "fa_b200_strerror", "fa_b200_device_ok",
            "fa_b200_last_status", "fa_b200_abi_version", "fa_b200_decode", "fa_b200_decode_workspace_bytes", "fa_b200_decode_static",
-           "fa_b200_add_layernorm")
+           "fa_b200_add_layernorm", "fa_b200_linear_small")
 
 _lib = None
 
@@ -86,6 +95,8 @@ def load() -> ctypes.CDLL:
     lib.fa_b200_decode_workspace_bytes.restype = ctypes.c_int64
     lib.fa_b200_add_layernorm.argtypes = [ctypes.POINTER(FaAddLnParams)]
     lib.fa_b200_add_layernorm.restype = ctypes.c_int
+    lib.fa_b200_linear_small.argtypes = [ctypes.POINTER(FaLinearSmallParams)]
+    lib.fa_b200_linear_small.restype = ctypes.c_int
     lib.fa_b200_abi_version.argtypes = []
     lib.fa_b200_abi_version.restype = ctypes.c_int
     if lib.fa_b200_abi_version() != ABI_VERSION:

@@ -13,7 +13,9 @@ import torch
 
 from . import _lib
 
-__all__ = ["add_layernorm"]
+__all__ = ["add_layernorm", "linear_small", "LINEAR_SMALL_MAX_ROWS"]
+
+LINEAR_SMALL_MAX_ROWS = 8
 
 
 def _dense2d(t: torch.Tensor, name: str, cols: int) -> torch.Tensor:
@@ -56,3 +58,35 @@ def add_layernorm(a, resid, scale, shift, eps: float = 1e-5, return_sum: bool = 
     if rc != 0:
         raise RuntimeError(_lib.strerror(rc))
     return (sum_out, norm_out) if keep else norm_out
+
+
+def linear_small(x, weight, bias=None, gelu: bool = False, out=None):
+    """`act(x @ weight.T + bias)` for at most 8 rows of x: `weight` [N, K] as nn.Linear stores it
+    (rows may be strided), `x` [..., K] with at most 8 rows in total, tanh-GELU when `gelu`.
+    One pass over the weights (`fa_b200_linear_small`)."""
+    K = x.shape[-1]
+    _dense2d(x, "x", K)
+    M = x.numel() // K
+    if not (weight.is_cuda and weight.dtype == torch.bfloat16 and weight.dim() == 2 and weight.shape[1] == K
+            and weight.stride(1) == 1):
+        raise RuntimeError("weight must be a CUDA bfloat16 matrix [N, K] with dense rows")
+    N = weight.shape[0]
+    if bias is not None and not (bias.is_cuda and bias.dtype == torch.bfloat16 and bias.numel() == N
+                                 and bias.is_contiguous()):
+        raise RuntimeError("bias must be a contiguous CUDA bfloat16 vector of N elements")
+    if out is None:
+        out = torch.empty(*x.shape[:-1], N, dtype=torch.bfloat16, device=x.device)
+    elif out.shape[-1] != N or out.numel() != M * N or not out.is_contiguous() or out.dtype != torch.bfloat16:
+        raise RuntimeError("out must be a contiguous bfloat16 tensor [..., N]")
+    p = _lib.FaLinearSmallParams()
+    p.x, p.w, p.y = x.data_ptr(), weight.data_ptr(), out.data_ptr()
+    p.bias = bias.data_ptr() if bias is not None else None
+    p.M, p.N, p.K = M, N, K
+    p.ldw = weight.stride(0) if N > 1 else K
+    p.act = 1 if gelu else 0
+    p.device = x.device.index
+    p.stream = torch.cuda.current_stream(x.device).cuda_stream
+    rc = _lib.load().fa_b200_linear_small(ctypes.byref(p))
+    if rc != 0:
+        raise RuntimeError(_lib.strerror(rc))
+    return out

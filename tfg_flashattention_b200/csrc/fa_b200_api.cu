@@ -14,6 +14,7 @@
 #include "add_layernorm_sm100.cuh"
 #include "fa_decode_sm100.cuh"
 #include "fa_fwd_sm100.cuh"
+#include "linear_small_sm100.cuh"
 
 namespace {
 
@@ -29,6 +30,7 @@ struct DeviceState {
   int init_error = 0;       // value fa_b200_fwd returns if set-up failed
   unsigned int* status = nullptr;  // device address of the watchdog words
   int resident_ctas = 0;           // persistent grid size: CTAs per SM x SM count
+  int sm_count = 0;
 };
 
 DeviceState g_dev[kMaxDevices];
@@ -103,6 +105,7 @@ void init_device(int dev) {
   // has been seen to answer 1 where the hardware co-schedules 2, and a CTA that has to wait for
   // a slot only starts later -- work items are partitioned by grid stride, no CTA waits on another.
   st.resident_ctas = fa::kCtasPerSm * prop.multiProcessorCount;
+  st.sm_count = prop.multiProcessorCount;
   void* addr = nullptr;
   e = cudaGetSymbolAddress(&addr, g_fa_status);
   if (e != cudaSuccess) { st.init_error = static_cast<int>(e); return; }
@@ -497,6 +500,82 @@ int fa_b200_add_layernorm(const fa_b200_add_layernorm_params* p) {
     case 6: e = launch_add_ln<6>(kp, stream); break;
     case 7: e = launch_add_ln<7>(kp, stream); break;
     default: e = launch_add_ln<8>(kp, stream); break;
+  }
+  return static_cast<int>(e);
+}
+
+// ------------------------------------------------------------------- Linear for a few rows
+extern "C++" {
+namespace {
+
+constexpr int kLinSmemLimit = 128 * 1024;
+std::once_flag g_lin_once[kMaxDevices];
+int g_lin_error[kMaxDevices];
+
+template <int kRows>
+cudaError_t lin_prepare() {
+  return cudaFuncSetAttribute(reinterpret_cast<const void*>(&fa::fa_linear_small_kernel<kRows>),
+                              cudaFuncAttributeMaxDynamicSharedMemorySize, kLinSmemLimit);
+}
+void lin_init(int dev) {   // with `dev` current
+  cudaError_t e = lin_prepare<1>();
+  if (e == cudaSuccess) e = lin_prepare<2>();
+  if (e == cudaSuccess) e = lin_prepare<4>();
+  if (e == cudaSuccess) e = lin_prepare<8>();
+  g_lin_error[dev] = static_cast<int>(e);
+}
+template <int kRows>
+cudaError_t lin_launch(const fa::LinearSmallParams& kp, cudaStream_t stream, int sm_count) {
+  const size_t smem = static_cast<size_t>(kRows) * kp.K * 2;
+  // as many CTAs per SM as ~200 KB of shared memory hold (1..8): every CTA stages x once
+  long long per_sm = (200 * 1024) / static_cast<long long>(smem > 0 ? smem : 1);
+  per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
+  long long ctas = (kp.N + fa::kLinWarps - 1) / fa::kLinWarps;
+  if (ctas > per_sm * sm_count) ctas = per_sm * sm_count;
+  fa::fa_linear_small_kernel<kRows><<<static_cast<unsigned>(ctas), fa::kLinWarps * 32, smem, stream>>>(kp);
+  return cudaGetLastError();
+}
+
+}  // namespace
+}  // extern "C++"
+
+int fa_b200_linear_small(const fa_b200_linear_small_params* p) {
+  if (p == nullptr || p->x == nullptr || p->w == nullptr || p->y == nullptr) return FA_B200_ERR_NULL;
+  if (p->M < 1 || p->M > fa::kLinMaxRows || p->N < 0 || p->K <= 0 || (p->K % 8) != 0)
+    return FA_B200_ERR_SHAPE;
+  const int rows = p->M <= 1 ? 1 : (p->M <= 2 ? 2 : (p->M <= 4 ? 4 : 8));
+  if (static_cast<long long>(rows) * p->K * 2 > kLinSmemLimit) return FA_B200_ERR_SHAPE;
+  if (p->act != 0 && p->act != 1) return FA_B200_ERR_SHAPE;
+  if (p->ldw < p->K || (p->ldw % 8) != 0) return FA_B200_ERR_STRIDE;
+  if ((reinterpret_cast<uintptr_t>(p->x) & 15u) || (reinterpret_cast<uintptr_t>(p->w) & 15u) ||
+      (reinterpret_cast<uintptr_t>(p->y) & 15u) || (reinterpret_cast<uintptr_t>(p->bias) & 1u))
+    return FA_B200_ERR_ALIGN;
+  if (p->device < 0 || p->device >= kMaxDevices) return FA_B200_ERR_DEVICE;
+  if (p->N == 0) return FA_B200_OK;
+
+  DeviceGuard guard(p->device);
+  if (guard.error) return guard.error;
+  DeviceState& st = g_dev[p->device];
+  std::call_once(st.once, init_device, p->device);
+  if (st.init_error) return st.init_error;
+  std::call_once(g_lin_once[p->device], lin_init, p->device);
+  if (g_lin_error[p->device]) return g_lin_error[p->device];
+
+  fa::LinearSmallParams kp;
+  kp.x = static_cast<const __nv_bfloat16*>(p->x);
+  kp.w = static_cast<const __nv_bfloat16*>(p->w);
+  kp.bias = static_cast<const __nv_bfloat16*>(p->bias);
+  kp.y = static_cast<__nv_bfloat16*>(p->y);
+  kp.M = p->M; kp.N = p->N; kp.K = p->K;
+  kp.ldw = p->ldw;
+  kp.act = p->act;
+  const cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+  cudaError_t e;
+  switch (rows) {
+    case 1: e = lin_launch<1>(kp, stream, st.sm_count); break;
+    case 2: e = lin_launch<2>(kp, stream, st.sm_count); break;
+    case 4: e = lin_launch<4>(kp, stream, st.sm_count); break;
+    default: e = lin_launch<8>(kp, stream, st.sm_count); break;
   }
   return static_cast<int>(e);
 }

@@ -61,6 +61,16 @@ def gpt2_config(name: str, impl_type: str = "cuda", context_length: int = 1024) 
     return cfg
 
 
+def _few_rows(x, enabled, limit=1) -> bool:
+    """True when `x` holds at most `limit` token rows on the bf16 GPU path: its Linear layer then
+    goes through block_ops.linear_small (one pass over the weights) instead of a tiled GEMM.
+    Measured on B200 against cuBLAS inside CUDA graphs: for one row the kernel is equal (QKV, first
+    MLP layer) or up to 2x faster (K = 4 * d_model, d_model x d_model, the vocabulary head); from
+    two rows on cuBLAS wins on the wide layers, except for the head (faster up to 8 rows)."""
+    return (enabled and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0
+            and x.numel() // x.shape[-1] <= limit and x.shape[-1] <= 8192)
+
+
 class DevicePosition:
     """Where the next token goes, kept on the GPU so that a recorded decode step needs no host
     value: `index` (int64 [1]) addresses the cache row and the position embedding, `length`
@@ -95,6 +105,7 @@ class MultiHeadAttention(nn.Module):
         self.context_length = context_length
         self._qkv_w = None      # fused [3*d_out, d_in] weight / [3*d_out] bias (inference cache)
         self._qkv_b = None
+        self.small_linear = False   # set by GPTModel.prepare_for_inference on the bf16 GPU path
 
     def fuse_qkv(self):
         """Cache the concatenated projection (call again after changing the weights)."""
@@ -109,8 +120,12 @@ class MultiHeadAttention(nn.Module):
         pos .. pos+n-1 and the queries attend rows 0 .. pos+n-1 (causally among themselves)."""
         b, n, _ = x.shape
         h, d = self.num_heads, self.head_dim
+        few = _few_rows(x, self.small_linear and not self.training)
+        if few:
+            from .block_ops import linear_small
         if self._qkv_w is not None and not self.training:
-            qkv = F.linear(x, self._qkv_w, self._qkv_b).view(b, n, 3, h, d)
+            qkv = (linear_small(x.contiguous(), self._qkv_w, self._qkv_b) if few
+                   else F.linear(x, self._qkv_w, self._qkv_b)).view(b, n, 3, h, d)
             q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
         else:
             q = self.W_query(x).view(b, n, h, d).transpose(1, 2)
@@ -155,6 +170,8 @@ class MultiHeadAttention(nn.Module):
         ctx = ctx.reshape(b, n, self.d_out)
         if not torch.is_autocast_enabled():
             ctx = ctx.to(self.out_proj.weight.dtype)
+        if few and ctx.dtype == torch.bfloat16:
+            return linear_small(ctx.contiguous(), self.out_proj.weight, self.out_proj.bias)
         return self.out_proj(ctx)
 
 
@@ -180,8 +197,14 @@ class FeedForward(nn.Module):
         self.layers = nn.Sequential(nn.Linear(config["emb_dim"], 4 * config["emb_dim"]), GELU(),
                                     nn.Linear(4 * config["emb_dim"], config["emb_dim"]))
 
+    small_linear = False   # set by GPTModel.prepare_for_inference on the bf16 GPU path
+
     def forward(self, x):
         fc, proj = self.layers[0], self.layers[2]
+        if _few_rows(x, self.small_linear and not self.training) and fc.weight.dtype == x.dtype:
+            from .block_ops import linear_small
+            h = linear_small(x.contiguous(), fc.weight, fc.bias, gelu=True)
+            return linear_small(h, proj.weight, proj.bias)
         if x.is_cuda and x.dtype == torch.bfloat16 and not self.training and fc.weight.dtype == x.dtype:
             # the tanh GELU runs in the epilogue of the first GEMM (cuBLASLt) instead of as a
             # separate pass over the [tokens, 4*d_model] activation
@@ -245,12 +268,15 @@ class GPTModel(nn.Module):
         d = self.cfg["emb_dim"]
         self._fused_blocks = (w.is_cuda and w.dtype == torch.bfloat16 and self.cfg["impl_type"] == "cuda"
                               and d % 8 == 0 and d <= 2048 and self.cfg["drop_rate"] == 0.0)
+        for blk in self.trf_blocks:      # single-token steps: Linear layers as one pass over the weights
+            blk.att.small_linear = blk.ff.small_linear = self._fused_blocks
         return self
 
     def invalidate_inference_cache(self):
         """Drop the derived tensors of `prepare_for_inference` (after the parameters changed)."""
         for blk in self.trf_blocks:
             blk.att._qkv_w = blk.att._qkv_b = None
+            blk.att.small_linear = blk.ff.small_linear = False
         self._head_w = None
         self._fused_blocks = False
         return self
@@ -363,6 +389,9 @@ class GPTModel(nn.Module):
             x = self.final_norm(x)
             if last_token_only:           # what generate() consumes (model_inference.py:206)
                 x = x[:, -1:, :]
+        if _few_rows(x, self._fused_blocks and not self.training, limit=8):
+            from .block_ops import linear_small
+            return linear_small(x.contiguous(), self.out_head.weight)
         if self._head_w is not None and not self.training:
             return F.linear(x, self._head_w)[..., :self.out_head.weight.shape[0]]
         return self.out_head(x)
