@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define FA_B200_ABI_VERSION 2
+#define FA_B200_ABI_VERSION 3
 
 /* argument errors (negative return values) */
 #define FA_B200_OK                 0
@@ -52,6 +52,7 @@ extern "C" {
 #define FA_B200_ERR_BUILD        -11  /* kernel image / launch configuration mismatch         */
 #define FA_B200_ERR_WORKSPACE    -12  /* decode workspace NULL, too small or misaligned    */
 #define FA_B200_ERR_STATIC_SCRATCH -13 /* problem needs more than FA_B200_STATIC_SCRATCH_BYTES */
+#define FA_B200_ERR_ALIAS        -14  /* an output overlaps an input it must not overlap   */
 
 typedef struct fa_b200_params {
   const void* q;            /* bf16 [B,H,N,d] */
@@ -136,6 +137,15 @@ typedef struct fa_b200_decode_params {
    * the device.  kv_len is then the upper bound the launch is sized for (grid, workspace); the
    * value read is clamped to [1, kv_len]. */
   const int32_t* kv_len_device;
+  /* Optional (ABI version 3): the cache append of the step, folded into the kernel.  When k_new
+   * is not NULL, k_new / v_new are bf16 [B, H, 64] (element strides new_strides = {batch, head},
+   * multiples of 8; 16-byte aligned) holding the key / value of the token being generated: the
+   * kernel uses them as row (length - 1), where length is kv_len or the value read through
+   * kv_len_device, and stores them into that row of k_cache / v_cache (which it therefore
+   * writes).  Both or neither. */
+  const void* k_new;
+  const void* v_new;
+  int64_t     new_strides[2];
 } fa_b200_decode_params;
 
 /* Bytes of workspace fa_b200_decode needs for this problem size (0 when the keys of a head are
@@ -225,6 +235,19 @@ typedef struct fa_b200_linear_small_params {
   int32_t act;
   int32_t device;
   void* stream;
+  /* Optional prologue on x, fused into the kernel (all NULL = none; needs K <= 2048):
+   *   x <- x + resid               resid [M, K] bf16 or NULL
+   *   sum_out <- bf16(x)           [M, K] or NULL: the new residual stream; must not be x or resid
+   *   x <- LayerNorm(x) * ln_scale + ln_shift     ln_scale / ln_shift [K] bf16, both or neither
+   * i.e. fa_b200_add_layernorm followed by this layer, without the separate kernel: the shortcut
+   * addition and LayerNorm that precede the QKV projection, the first MLP layer and the output
+   * head in the reference's block (src/py/model_inference.py:102-107, 153-163, 188-190).  When
+   * sum_out is given, the normalised row is the bf16-rounded sum. */
+  const void* resid;
+  const void* ln_scale;
+  const void* ln_shift;
+  void* sum_out;
+  float eps;
 } fa_b200_linear_small_params;
 
 int fa_b200_linear_small(const fa_b200_linear_small_params* p);

@@ -159,3 +159,11 @@ def test_linear_small_rejects_before_any_cuda_call(fa_lib):
     assert call(params(x=0x1008)) == -5
     assert call(params(device=-1)) == -7
     assert call(params(N=0)) == 0
+    # the fused add + LayerNorm prologue
+    assert call(params(ln_scale=0x5000)) == -1                       # scale without shift
+    assert call(params(K=4096, ldw=4096, ln_scale=0x5000, ln_shift=0x6000)) == -3
+    assert call(params(resid=0x5008)) == -5
+    assert call(params(resid=0x5000, sum_out=0x5000)) == -14         # sum over its own input
+    assert call(params(resid=0x5000, sum_out=0x1000)) == -14
+    assert call(params(ln_scale=0x5000, ln_shift=0x6000, eps=-1.0)) == -6
+    assert b"overlap" in fa_lib.fa_b200_strerror(-14)

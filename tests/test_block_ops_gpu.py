@@ -124,3 +124,49 @@ def test_linear_small_strided_weight_3d_input_and_errors(fa_lib):
         linear_small(torch.zeros(2, 60, device="cuda").bfloat16(), torch.zeros(8, 60, device="cuda").bfloat16())
     with pytest.raises(RuntimeError):
         linear_small(x, w.float())
+
+
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("K", [64, 768, 1600, 2048])
+def test_linear_small_with_add_layernorm_prologue(fa_lib, M, K):
+    """x' = LayerNorm(x + resid) inside the Linear kernel: equal to add_layernorm followed by the
+    plain kernel (same roundings), and close to the fp32 formula."""
+    from tfg_flashattention_b200.block_ops import add_layernorm, linear_small
+    g = torch.Generator(device="cuda").manual_seed(M * 7919 + K)
+    N = 3 * K if K <= 768 else 264
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    r = (torch.randn(M, K, device="cuda", generator=g) * 2).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).bfloat16()
+    b = torch.randn(N, device="cuda", generator=g).bfloat16()
+    sc = (1 + 0.2 * torch.randn(K, device="cuda", generator=g)).bfloat16()
+    sh = (0.3 * torch.randn(K, device="cuda", generator=g)).bfloat16()
+    # with the sum kept
+    s_ref, h_ref = add_layernorm(x, r, sc, sh, 1e-5)
+    y_ref = linear_small(h_ref, w, b, gelu=True)
+    s, y = linear_small(x, w, b, gelu=True, resid=r, ln_scale=sc, ln_shift=sh, eps=1e-5, keep_sum=True)
+    assert torch.equal(s, s_ref)
+    torch.testing.assert_close(y.float(), y_ref.float(), rtol=0, atol=2e-2)
+    assert (y.float() - y_ref.float()).abs().mean().item() < 1e-3
+    # LayerNorm only (first block, final norm without residual) and residual only
+    y1 = linear_small(x, w, b, ln_scale=sc, ln_shift=sh)
+    y1_ref = linear_small(add_layernorm(x, None, sc, sh, 1e-5), w, b)
+    torch.testing.assert_close(y1.float(), y1_ref.float(), rtol=0, atol=2e-2)
+    y2 = linear_small(x, w, resid=r)
+    y2_ref = (x.float() + r.float()) @ w.float().t()
+    assert ((y2.float() - y2_ref).abs() <= 2.0 ** -7 * y2_ref.abs() + 3e-2).all()
+    # fp32 formula end to end
+    s32 = (x.float() + r.float()).bfloat16().float()
+    h32 = torch.nn.functional.layer_norm(s32, (K,), sc.float(), sh.float(), 1e-5).bfloat16().float()
+    want = torch.nn.functional.gelu(h32 @ w.float().t() + b.float(), approximate="tanh")
+    assert ((y.float() - want).abs() <= 2.0 ** -6 * want.abs() + 2e-2).all()
+
+
+def test_linear_small_prologue_rejects(fa_lib):
+    from tfg_flashattention_b200.block_ops import linear_small
+    x = torch.zeros(1, 4096, device="cuda").bfloat16()
+    w = torch.zeros(8, 4096, device="cuda").bfloat16()
+    one = torch.ones(4096, device="cuda").bfloat16()
+    with pytest.raises(RuntimeError, match="fa_b200"):
+        linear_small(x, w, ln_scale=one, ln_shift=one)            # K > 2048 with a prologue
+    with pytest.raises(RuntimeError):
+        linear_small(x[:, :64].contiguous(), w[:, :64].contiguous(), ln_scale=one[:64].contiguous())

@@ -196,3 +196,33 @@ def test_generation_with_graph_replay_equals_eager_cache_path(golden_dir, fa_lib
                        gpt2.generate(m, prompt2, 9, 128, temperature=0.0))
     from tfg_flashattention_b200 import custom_flash_attn
     assert custom_flash_attn.last_status() == 0
+
+
+@pytest.mark.gpu
+def test_decode_appends_the_new_row_itself(fa_lib):
+    """k_new / v_new: the kernel uses them as the newest row and writes them into the caches;
+    same result as copying them in first, for host- and device-side lengths, split and unsplit."""
+    from tfg_flashattention_b200 import custom_flash_attn as cfa
+    torch.manual_seed(4)
+    for B, H, cap, n in ((2, 3, 300, 137), (32, 25, 128, 128), (1, 2, 1000, 1), (1, 25, 1024, 700)):
+        q = torch.randn(B, H, 64, device="cuda").bfloat16()
+        k = torch.randn(B, H, cap, 64, device="cuda").bfloat16()
+        v = torch.randn(B, H, cap, 64, device="cuda").bfloat16()
+        qkv = torch.randn(B, 1, 3, H, 64, device="cuda").bfloat16()       # as the fused projection leaves them
+        kn, vn = qkv[:, :, 1].transpose(1, 2), qkv[:, :, 2].transpose(1, 2)   # [B, H, 1, 64] views
+        k_ref, v_ref = k.clone(), v.clone()
+        k_ref[:, :, n - 1] = kn[:, :, 0]
+        v_ref[:, :, n - 1] = vn[:, :, 0]
+        want, lse_want = cfa.decode(q, k_ref, v_ref, n, return_lse=True)
+        k1, v1 = k.clone(), v.clone()
+        got, lse = cfa.decode(q, k1, v1, n, return_lse=True, k_new=kn, v_new=vn)
+        assert torch.equal(got, want) and torch.equal(lse, lse_want)
+        assert torch.equal(k1, k_ref) and torch.equal(v1, v_ref)        # appended, nothing else touched
+        k2, v2 = k.clone(), v.clone()
+        length = torch.full((1,), n, dtype=torch.int32, device="cuda")
+        got2 = cfa.decode(q, k2, v2, length, k_new=kn, v_new=vn)
+        assert torch.equal(k2, k_ref) and torch.equal(v2, v_ref)
+        torch.testing.assert_close(got2.float(), want.float(), rtol=0, atol=2e-2)
+    assert cfa.last_status() == 0
+    with pytest.raises(RuntimeError):
+        cfa.decode(q, k, v, 5, k_new=kn)

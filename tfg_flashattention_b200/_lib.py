@@ -10,7 +10,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libfa_b200.so")
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 
 class FaParams(ctypes.Structure):
@@ -37,6 +37,7 @@ class FaDecodeParams(ctypes.Structure):
         ("k_strides", ctypes.c_int64 * 3), ("v_strides", ctypes.c_int64 * 3),
         ("softmax_scale", ctypes.c_float), ("device", ctypes.c_int32), ("stream", ctypes.c_void_p),
         ("kv_len_device", ctypes.c_void_p),
+        ("k_new", ctypes.c_void_p), ("v_new", ctypes.c_void_p), ("new_strides", ctypes.c_int64 * 2),
     ]
 
 
@@ -56,6 +57,8 @@ class FaLinearSmallParams(ctypes.Structure):
         ("x", ctypes.c_void_p), ("w", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("y", ctypes.c_void_p),
         ("M", ctypes.c_int32), ("N", ctypes.c_int32), ("K", ctypes.c_int32), ("ldw", ctypes.c_int64),
         ("act", ctypes.c_int32), ("device", ctypes.c_int32), ("stream", ctypes.c_void_p),
+        ("resid", ctypes.c_void_p), ("ln_scale", ctypes.c_void_p), ("ln_shift", ctypes.c_void_p),
+        ("sum_out", ctypes.c_void_p), ("eps", ctypes.c_float),
     ]
 
 

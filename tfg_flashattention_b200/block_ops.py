@@ -60,10 +60,15 @@ def add_layernorm(a, resid, scale, shift, eps: float = 1e-5, return_sum: bool = 
     return (sum_out, norm_out) if keep else norm_out
 
 
-def linear_small(x, weight, bias=None, gelu: bool = False, out=None):
-    """`act(x @ weight.T + bias)` for at most 8 rows of x: `weight` [N, K] as nn.Linear stores it
-    (rows may be strided), `x` [..., K] with at most 8 rows in total, tanh-GELU when `gelu`.
-    One pass over the weights (`fa_b200_linear_small`)."""
+def linear_small(x, weight, bias=None, gelu: bool = False, out=None, resid=None, ln_scale=None,
+                 ln_shift=None, eps: float = 1e-5, keep_sum: bool = False):
+    """`act(x' @ weight.T + bias)` for at most 8 rows: `weight` [N, K] as nn.Linear stores it (rows
+    may be strided), `x` [..., K] with at most 8 rows in total, tanh-GELU when `gelu`.  One pass
+    over the weights (`fa_b200_linear_small`).
+
+    Optional prologue inside the same kernel (K <= 2048): `x' = x + resid`, then
+    `x' = LayerNorm(x') * ln_scale + ln_shift`; with `keep_sum` the sum `x + resid` is also
+    returned (a new bf16 tensor: the next residual stream) and the result is `(sum, y)`."""
     K = x.shape[-1]
     _dense2d(x, "x", K)
     M = x.numel() // K
@@ -74,19 +79,36 @@ def linear_small(x, weight, bias=None, gelu: bool = False, out=None):
     if bias is not None and not (bias.is_cuda and bias.dtype == torch.bfloat16 and bias.numel() == N
                                  and bias.is_contiguous()):
         raise RuntimeError("bias must be a contiguous CUDA bfloat16 vector of N elements")
+    if resid is not None:
+        _dense2d(resid, "resid", K)
+        if resid.shape != x.shape:
+            raise RuntimeError("x and resid must have the same shape")
+    if (ln_scale is None) != (ln_shift is None):
+        raise RuntimeError("ln_scale and ln_shift go together")
+    for t, name in ((ln_scale, "ln_scale"), (ln_shift, "ln_shift")):
+        if t is not None:
+            _dense2d(t, name, K)
+            if t.numel() != K:
+                raise RuntimeError(f"{name} must have {K} elements")
     if out is None:
         out = torch.empty(*x.shape[:-1], N, dtype=torch.bfloat16, device=x.device)
     elif out.shape[-1] != N or out.numel() != M * N or not out.is_contiguous() or out.dtype != torch.bfloat16:
         raise RuntimeError("out must be a contiguous bfloat16 tensor [..., N]")
+    total = torch.empty_like(x) if keep_sum else None
     p = _lib.FaLinearSmallParams()
     p.x, p.w, p.y = x.data_ptr(), weight.data_ptr(), out.data_ptr()
     p.bias = bias.data_ptr() if bias is not None else None
     p.M, p.N, p.K = M, N, K
     p.ldw = weight.stride(0) if N > 1 else K
     p.act = 1 if gelu else 0
+    p.resid = resid.data_ptr() if resid is not None else None
+    p.ln_scale = ln_scale.data_ptr() if ln_scale is not None else None
+    p.ln_shift = ln_shift.data_ptr() if ln_shift is not None else None
+    p.sum_out = total.data_ptr() if total is not None else None
+    p.eps = eps
     p.device = x.device.index
     p.stream = torch.cuda.current_stream(x.device).cuda_stream
     rc = _lib.load().fa_b200_linear_small(ctypes.byref(p))
     if rc != 0:
         raise RuntimeError(_lib.strerror(rc))
-    return out
+    return (total, out) if keep_sum else out

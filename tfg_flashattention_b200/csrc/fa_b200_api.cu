@@ -273,6 +273,12 @@ int decode_validate(const fa_b200_decode_params* p) {
     if (a & 15u) return FA_B200_ERR_ALIGN;
   if (p->lse != nullptr && (reinterpret_cast<uintptr_t>(p->lse) & 3u)) return FA_B200_ERR_ALIGN;
   if (p->kv_len_device != nullptr && (reinterpret_cast<uintptr_t>(p->kv_len_device) & 3u)) return FA_B200_ERR_ALIGN;
+  if ((p->k_new == nullptr) != (p->v_new == nullptr)) return FA_B200_ERR_NULL;
+  if (p->k_new != nullptr) {
+    if (!stride_ok_n(p->new_strides, 2)) return FA_B200_ERR_STRIDE;
+    if ((reinterpret_cast<uintptr_t>(p->k_new) & 15u) || (reinterpret_cast<uintptr_t>(p->v_new) & 15u))
+      return FA_B200_ERR_ALIGN;
+  }
   if (!(p->softmax_scale >= 0.0f) || std::isinf(p->softmax_scale)) return FA_B200_ERR_SCALE;
   if (p->device < 0 || p->device >= kMaxDevices) return FA_B200_ERR_DEVICE;
   return FA_B200_OK;
@@ -320,6 +326,9 @@ int fa_b200_decode(const fa_b200_decode_params* p) {
   kp.v_sb = p->v_strides[0]; kp.v_sh = p->v_strides[1]; kp.v_sn = p->v_strides[2];
   kp.B = p->B; kp.H = p->H; kp.kv_len = p->kv_len;
   kp.kv_len_ptr = p->kv_len_device;
+  kp.k_new = static_cast<const __nv_bfloat16*>(p->k_new);
+  kp.v_new = static_cast<const __nv_bfloat16*>(p->v_new);
+  kp.new_sb = p->new_strides[0]; kp.new_sh = p->new_strides[1];
   kp.splits = splits;
   kp.rows_per_split = rows;
   const float scale = p->softmax_scale > 0.0f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(p->d));
@@ -395,6 +404,9 @@ int fa_b200_decode_static(const fa_b200_decode_params* p) {
   kp.v_sb = p->v_strides[0]; kp.v_sh = p->v_strides[1]; kp.v_sn = p->v_strides[2];
   kp.B = p->B; kp.H = p->H; kp.kv_len = p->kv_len;
   kp.kv_len_ptr = p->kv_len_device;
+  kp.k_new = static_cast<const __nv_bfloat16*>(p->k_new);
+  kp.v_new = static_cast<const __nv_bfloat16*>(p->v_new);
+  kp.new_sb = p->new_strides[0]; kp.new_sh = p->new_strides[1];
   kp.splits = splits;
   kp.rows_per_split = rows;
   const float scale = p->softmax_scale > 0.0f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(p->d));
@@ -550,6 +562,16 @@ int fa_b200_linear_small(const fa_b200_linear_small_params* p) {
   if ((reinterpret_cast<uintptr_t>(p->x) & 15u) || (reinterpret_cast<uintptr_t>(p->w) & 15u) ||
       (reinterpret_cast<uintptr_t>(p->y) & 15u) || (reinterpret_cast<uintptr_t>(p->bias) & 1u))
     return FA_B200_ERR_ALIGN;
+  const bool prologue = p->resid != nullptr || p->ln_scale != nullptr || p->sum_out != nullptr;
+  if (prologue) {
+    if ((p->ln_scale == nullptr) != (p->ln_shift == nullptr)) return FA_B200_ERR_NULL;
+    if (p->K > 256 * 8) return FA_B200_ERR_SHAPE;
+    const void* extra[4] = {p->resid, p->ln_scale, p->ln_shift, p->sum_out};
+    for (const void* q : extra)
+      if (reinterpret_cast<uintptr_t>(q) & 15u) return FA_B200_ERR_ALIGN;
+    if (p->sum_out != nullptr && (p->sum_out == p->x || p->sum_out == p->resid)) return FA_B200_ERR_ALIAS;
+    if (p->ln_scale != nullptr && !(p->eps >= 0.0f)) return FA_B200_ERR_SCALE;
+  }
   if (p->device < 0 || p->device >= kMaxDevices) return FA_B200_ERR_DEVICE;
   if (p->N == 0) return FA_B200_OK;
 
@@ -569,6 +591,11 @@ int fa_b200_linear_small(const fa_b200_linear_small_params* p) {
   kp.M = p->M; kp.N = p->N; kp.K = p->K;
   kp.ldw = p->ldw;
   kp.act = p->act;
+  kp.resid = static_cast<const __nv_bfloat16*>(p->resid);
+  kp.ln_scale = static_cast<const __nv_bfloat16*>(p->ln_scale);
+  kp.ln_shift = static_cast<const __nv_bfloat16*>(p->ln_shift);
+  kp.sum_out = static_cast<__nv_bfloat16*>(p->sum_out);
+  kp.eps = p->eps;
   const cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
   cudaError_t e;
   switch (rows) {
@@ -607,6 +634,7 @@ const char* fa_b200_strerror(int code) {
     case FA_B200_ERR_TENSORMAP: return "fa_b200: the driver rejected a TMA tensor map (check strides and sizes)";
     case FA_B200_ERR_DRIVER: return "fa_b200: cuTensorMapEncodeTiled is not available from this driver";
     case FA_B200_ERR_STATIC_SCRATCH: return "fa_b200: this decode problem needs more split-KV scratch than the built-in buffer holds (FA_B200_STATIC_SCRATCH_BYTES); use fa_b200_decode with a workspace";
+    case FA_B200_ERR_ALIAS: return "fa_b200: an output buffer overlaps an input it must not overlap";
     case FA_B200_ERR_WORKSPACE: return "fa_b200: decode workspace is NULL, too small or not 16-byte aligned";
     case FA_B200_ERR_BUILD: return "fa_b200: the kernel image does not match this library's launch configuration; rebuild it";
     default: break;

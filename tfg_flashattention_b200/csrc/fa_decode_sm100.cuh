@@ -46,6 +46,12 @@ struct DecodeParams {
   int splits;                  // chunks per head
   int rows_per_split;          // multiple of kDecodeGroups
   float scale_log2;            // softmax_scale * log2(e)
+  // when set: the newest row (index length - 1) is taken from these [B, H, 64] buffers instead of
+  // the caches and written into the caches by the CTA that owns it (the cache append of a
+  // generation step, folded into the attention kernel)
+  const __nv_bfloat16* k_new = nullptr;
+  const __nv_bfloat16* v_new = nullptr;
+  long long new_sb = 0, new_sh = 0;
   const int* kv_len_ptr = nullptr;   // when set: the current length lives in device memory (read
                                      // at run time, clamped to [1, kv_len]); kv_len is the bound
                                      // the grid and the chunks were sized for
@@ -81,6 +87,8 @@ __global__ void __launch_bounds__(kDecodeThreads) fa_decode_partial_kernel(const
   }
   const __nv_bfloat16* kbase = p.k + b * p.k_sb + h * p.k_sh + 8 * c;
   const __nv_bfloat16* vbase = p.v + b * p.v_sb + h * p.v_sh + 8 * c;
+  const __nv_bfloat16* knew = p.k_new ? p.k_new + b * p.new_sb + h * p.new_sh + 8 * c : nullptr;
+  const __nv_bfloat16* vnew = p.k_new ? p.v_new + b * p.new_sb + h * p.new_sh + 8 * c : nullptr;
   const int kv_len = p.kv_len_ptr ? max(1, min(__ldg(p.kv_len_ptr), p.kv_len)) : p.kv_len;
   const int row_begin = split * p.rows_per_split;
   const int row_end = min(kv_len, row_begin + p.rows_per_split);   // chunks past the end stay empty
@@ -99,8 +107,13 @@ __global__ void __launch_bounds__(kDecodeThreads) fa_decode_partial_kernel(const
     for (int u = 0; u < kDecodeUnroll; ++u) {           // all loads first: rows in flight
       const int r = r0 + u * kDecodeGroups;
       if (r < row_end) {
-        kraw[u] = *reinterpret_cast<const uint4*>(kbase + (long long)r * p.k_sn);
-        vraw[u] = *reinterpret_cast<const uint4*>(vbase + (long long)r * p.v_sn);
+        const bool fresh = knew != nullptr && r == kv_len - 1;   // the row being appended
+        kraw[u] = *reinterpret_cast<const uint4*>(fresh ? knew : kbase + (long long)r * p.k_sn);
+        vraw[u] = *reinterpret_cast<const uint4*>(fresh ? vnew : vbase + (long long)r * p.v_sn);
+        if (fresh) {
+          *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(kbase) + (long long)r * p.k_sn) = kraw[u];
+          *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(vbase) + (long long)r * p.v_sn) = vraw[u];
+        }
       }
     }
 #pragma unroll

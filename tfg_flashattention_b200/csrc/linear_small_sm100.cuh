@@ -13,10 +13,18 @@
 // (8 bf16), four vectors in flight per lane, multiply with the matching slice of every x row
 // (staged once per CTA in shared memory) and reduce with shuffles.  The grid is a few CTAs per
 // SM; each warp takes several columns in turn.
+//
+// Optional prologue, fused into the staging of x: the shortcut addition and the LayerNorm that
+// precede the layer in a transformer block (x <- x + resid, the sum kept as the new residual
+// stream, x <- LayerNorm(x) * scale + shift; model_inference.py:102-107, 156, 163).  Every CTA
+// recomputes the statistics of the few rows (K <= 2048: one 16-byte vector per thread and row),
+// which removes a separate one-warp kernel from the dependency chain of a generation step.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+#include "add_layernorm_sm100.cuh"   // ln_unpack8 / ln_pack8 / ln_warp_sum
 
 namespace fa {
 
@@ -32,6 +40,12 @@ struct LinearSmallParams {
   int M, N, K;
   long long ldw;
   int act;                     // 0 none, 1 tanh-GELU
+  // optional prologue on x (K <= 2048): x <- x + resid; sum_out <- bf16(x); x <- LayerNorm(x)
+  const __nv_bfloat16* resid;      // [M, K] or null
+  const __nv_bfloat16* ln_scale;   // [K] or null: no LayerNorm
+  const __nv_bfloat16* ln_shift;   // [K]
+  __nv_bfloat16* sum_out;          // [M, K] or null; written by CTA 0 only; must not alias x / resid
+  float eps;
 };
 
 __device__ __forceinline__ float gelu_tanh(float v) {
@@ -44,10 +58,87 @@ template <int kRows>
 __global__ void __launch_bounds__(kLinWarps * 32) fa_linear_small_kernel(const LinearSmallParams p) {
   extern __shared__ uint4 lin_smem[];              // x: kRows rows of K/8 16-byte vectors
   const int nvec = p.K >> 3;
-  for (int i = threadIdx.x; i < kRows * nvec; i += kLinWarps * 32) {
-    const int m = i / nvec, v = i - m * nvec;
-    lin_smem[i] = m < p.M ? reinterpret_cast<const uint4*>(p.x + (long long)m * p.K)[v]
-                          : make_uint4(0u, 0u, 0u, 0u);
+  if (p.resid == nullptr && p.ln_scale == nullptr) {
+    for (int i = threadIdx.x; i < kRows * nvec; i += kLinWarps * 32) {
+      const int m = i / nvec, v = i - m * nvec;
+      lin_smem[i] = m < p.M ? reinterpret_cast<const uint4*>(p.x + (long long)m * p.K)[v]
+                            : make_uint4(0u, 0u, 0u, 0u);
+    }
+  } else {
+    // thread t owns vector t of every row (nvec <= 256, checked by the host)
+    __shared__ float red[2][kRows][kLinWarps];
+    const int v = threadIdx.x;
+    const bool live = v < nvec;
+    float xs[kRows][8];
+    float part[kRows];
+#pragma unroll
+    for (int m = 0; m < kRows; ++m) {
+      part[m] = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) xs[m][e] = 0.f;
+      if (live && m < p.M) {
+        ln_unpack8(reinterpret_cast<const uint4*>(p.x + (long long)m * p.K)[v], xs[m]);
+        if (p.resid) {
+          float r8[8];
+          ln_unpack8(reinterpret_cast<const uint4*>(p.resid + (long long)m * p.K)[v], r8);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) xs[m][e] += r8[e];
+        }
+        if (p.sum_out) {   // the kept sum is bf16: normalise exactly what its later readers see
+          const uint4 packed = ln_pack8(xs[m]);
+          if (blockIdx.x == 0) reinterpret_cast<uint4*>(p.sum_out + (long long)m * p.K)[v] = packed;
+          ln_unpack8(packed, xs[m]);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) part[m] += xs[m][e];
+      }
+    }
+    if (p.ln_scale) {
+      const int wid = threadIdx.x >> 5, ln_lane = threadIdx.x & 31;
+      float mean[kRows], rstd[kRows];
+#pragma unroll
+      for (int pass = 0; pass < 2; ++pass) {       // pass 0: mean; pass 1: variance about it
+#pragma unroll
+        for (int m = 0; m < kRows; ++m) {
+          const float w = ln_warp_sum(part[m]);
+          if (ln_lane == 0) red[pass][m][wid] = w;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int m = 0; m < kRows; ++m) {
+          float tot = 0.f;
+#pragma unroll
+          for (int i = 0; i < kLinWarps; ++i) tot += red[pass][m][i];
+          if (pass == 0) {
+            mean[m] = tot / (float)p.K;
+            part[m] = 0.f;
+            if (live && m < p.M) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const float d = xs[m][e] - mean[m];
+                part[m] = fmaf(d, d, part[m]);
+              }
+            }
+          } else {
+            rstd[m] = rsqrtf(tot / (float)p.K + p.eps);
+          }
+        }
+      }
+      if (live) {
+        float g[8], b[8];
+        ln_unpack8(__ldg(reinterpret_cast<const uint4*>(p.ln_scale) + v), g);
+        ln_unpack8(__ldg(reinterpret_cast<const uint4*>(p.ln_shift) + v), b);
+#pragma unroll
+        for (int m = 0; m < kRows; ++m) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) xs[m][e] = fmaf((xs[m][e] - mean[m]) * rstd[m], g[e], b[e]);
+        }
+      }
+    }
+    if (live) {
+#pragma unroll
+      for (int m = 0; m < kRows; ++m) lin_smem[m * nvec + v] = ln_pack8(xs[m]);   // rows >= M are zero
+    }
   }
   __syncthreads();
   const int lane = threadIdx.x & 31;

@@ -106,13 +106,17 @@ def forward(Q, K, V, causal=True, return_lse=False, softmax_scale=None, out=None
 _decode_workspaces = {}
 
 
-def decode(Q, K_cache, V_cache, kv_len, return_lse=False, softmax_scale=None, out=None):
+def decode(Q, K_cache, V_cache, kv_len, return_lse=False, softmax_scale=None, out=None,
+           k_new=None, v_new=None):
     """Single-query attention against a K/V cache (one generation step; the reference has no
     counterpart -- its generate() recomputes the whole prefix, model_inference.py:199-228).
 
     Q [B, H, 64] (or [B, H, 1, 64]) bf16; K_cache, V_cache [B, H, >= kv_len, 64] bf16 (any row /
     head / batch strides that are multiples of 8 elements); attends rows 0 .. kv_len-1.  kv_len is
     an int, or a one-element int32 CUDA tensor that is read by the kernel when it runs.
+    k_new, v_new [B, H, 64] (optional, both): the key / value of the token being generated; the
+    kernel uses them as row kv_len-1 and writes them into that row of the caches (the cache
+    append of the step without a separate copy kernel).
     Returns O shaped like Q (and LSE [B, H] fp32 when asked).  The split-KV workspace is a cached
     torch buffer per device; calls on one stream may share it, calls that overlap on different
     streams of one device must not (pass through separate processes or serialise them)."""
@@ -199,6 +203,17 @@ def decode(Q, K_cache, V_cache, kv_len, return_lse=False, softmax_scale=None, ou
     p.device = Q.device.index if Q.device.index is not None else torch.cuda.current_device()
     p.stream = torch.cuda.current_stream(Q.device).cuda_stream
     p.kv_len_device = kv_len_dev.data_ptr() if kv_len_dev is not None else None
+    if (k_new is None) != (v_new is None):
+        raise RuntimeError("k_new and v_new go together")
+    if k_new is not None:
+        kn = k_new[:, :, 0, :] if k_new.dim() == 4 else k_new
+        vn = v_new[:, :, 0, :] if v_new.dim() == 4 else v_new
+        for t, name in ((kn, "k_new"), (vn, "v_new")):
+            if not (t.is_cuda and t.dtype == torch.bfloat16 and t.shape == (B, H, d) and t.stride(-1) == 1):
+                raise RuntimeError(f"{name} must be a CUDA bfloat16 tensor [B, H, 64] with a dense last dimension")
+        if two(kn)[:] != two(vn)[:]:
+            raise RuntimeError("k_new and v_new must have the same strides")
+        p.k_new, p.v_new, p.new_strides = kn.data_ptr(), vn.data_ptr(), two(kn)
     rc = lib.fa_b200_decode(ctypes.byref(p))
     if rc != 0:
         raise RuntimeError(f"custom_flash_attn.decode failed ({rc}): {_lib.strerror(rc)}")

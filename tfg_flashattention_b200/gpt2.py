@@ -114,29 +114,42 @@ class MultiHeadAttention(nn.Module):
             self._qkv_b = (None if self.W_query.bias is None else
                            torch.cat([self.W_query.bias, self.W_key.bias, self.W_value.bias], 0).contiguous())
 
-    def forward(self, x, kv_cache=None, pos=0):
+    def forward(self, x, kv_cache=None, pos=0, qkv=None):
         """x [B, n, d_in].  Without a cache: causal attention among the n tokens (prefill).  With
         kv_cache = (K, V) of shape [B, N_max, H, d]: the new keys/values are written at rows
-        pos .. pos+n-1 and the queries attend rows 0 .. pos+n-1 (causally among themselves)."""
-        b, n, _ = x.shape
+        pos .. pos+n-1 and the queries attend rows 0 .. pos+n-1 (causally among themselves).
+        `qkv` [B, n, 3*d_out]: the fused projection already computed by the caller (x is unused)."""
         h, d = self.num_heads, self.head_dim
-        few = _few_rows(x, self.small_linear and not self.training)
-        if few:
+        if qkv is not None:
+            b, n = qkv.shape[:2]
+            few = True
             from .block_ops import linear_small
-        if self._qkv_w is not None and not self.training:
-            qkv = (linear_small(x.contiguous(), self._qkv_w, self._qkv_b) if few
-                   else F.linear(x, self._qkv_w, self._qkv_b)).view(b, n, 3, h, d)
+            qkv = qkv.view(b, n, 3, h, d)
             q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
         else:
-            q = self.W_query(x).view(b, n, h, d).transpose(1, 2)
-            k = self.W_key(x).view(b, n, h, d).transpose(1, 2)
-            v = self.W_value(x).view(b, n, h, d).transpose(1, 2)
+            b, n, _ = x.shape
+            few = _few_rows(x, self.small_linear and not self.training)
+            if few:
+                from .block_ops import linear_small
+            if self._qkv_w is not None and not self.training:
+                qkv = (linear_small(x.contiguous(), self._qkv_w, self._qkv_b) if few
+                       else F.linear(x, self._qkv_w, self._qkv_b)).view(b, n, 3, h, d)
+                q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+            else:
+                q = self.W_query(x).view(b, n, h, d).transpose(1, 2)
+                k = self.W_key(x).view(b, n, h, d).transpose(1, 2)
+                v = self.W_value(x).view(b, n, h, d).transpose(1, 2)
         dev_pos = isinstance(pos, DevicePosition)   # decode step inside a CUDA graph
         if dev_pos and not (self.impl_type == "cuda" and n == 1 and kv_cache is not None):
             raise NotImplementedError("a device-side position is for single-token steps of the cuda path")
+        # a single new token on the cuda path: the decode kernel appends k, v to the caches itself
+        append_in_kernel = (self.impl_type == "cuda" and kv_cache is not None and n == 1
+                            and k.dtype == torch.bfloat16 and kv_cache[0].dtype == torch.bfloat16)
         if kv_cache is not None:
             ck, cv = kv_cache
-            if dev_pos:
+            if append_in_kernel:
+                pass
+            elif dev_pos:
                 ck.index_copy_(1, pos.index, k.transpose(1, 2).to(ck.dtype))
                 cv.index_copy_(1, pos.index, v.transpose(1, 2).to(cv.dtype))
             else:
@@ -148,7 +161,9 @@ class MultiHeadAttention(nn.Module):
                 q, k, v = q.bfloat16(), k.bfloat16(), v.bfloat16()
             if kv_cache is not None and n == 1:
                 ctx = custom_flash_attn.decode(q, ck.transpose(1, 2), cv.transpose(1, 2),
-                                               pos.length if dev_pos else pos + 1)
+                                               pos.length if dev_pos else pos + 1,
+                                               k_new=k if append_in_kernel else None,
+                                               v_new=v if append_in_kernel else None)
                 ctx = ctx.transpose(1, 2)                                    # [B, 1, H, d]
             elif pos == 0:
                 ctx = custom_flash_attn.forward(q, k, v).transpose(1, 2)     # [B,N,H,d], dense
@@ -161,7 +176,7 @@ class MultiHeadAttention(nn.Module):
             total = pos + n if kv_cache is not None else n
             attn = q @ k.transpose(-2, -1)
             # query i (absolute position pos + i) sees keys 0 .. pos + i
-            mask = torch.triu(torch.ones(n, total, device=x.device), diagonal=1 + total - n).bool()
+            mask = torch.triu(torch.ones(n, total, device=q.device), diagonal=1 + total - n).bool()
             attn.masked_fill_(mask, -torch.inf)
             w = self.dropout(torch.softmax(attn / k.shape[-1] ** 0.5, dim=-1))
             ctx = (w @ v).transpose(1, 2)
@@ -316,6 +331,31 @@ class GPTModel(nn.Module):
         return add_layernorm(x if branch is None else branch, None if branch is None else x,
                              fn.scale, fn.shift, fn.eps, return_sum=False)
 
+    def _blocks_one_row(self, x, kv_caches, pos):
+        """The same stack for a single token row (a generation step at batch 1), returning the
+        LOGITS: every Linear layer is one pass over its weights (block_ops.linear_small) and the
+        "x + branch; LayerNorm" in front of the QKV projection, the first MLP layer and the head
+        runs inside that layer's kernel, so a block is five launches besides the cache append."""
+        from .block_ops import linear_small
+        branch = None
+        for i, blk in enumerate(self.trf_blocks):
+            cache = None if kv_caches is None else kv_caches[i]
+            att, fc, proj = blk.att, blk.ff.layers[0], blk.ff.layers[2]
+            if branch is None:
+                qkv = linear_small(x, att._qkv_w, att._qkv_b, ln_scale=blk.norm1.scale,
+                                   ln_shift=blk.norm1.shift, eps=blk.norm1.eps)
+            else:
+                x, qkv = linear_small(branch, att._qkv_w, att._qkv_b, resid=x, ln_scale=blk.norm1.scale,
+                                      ln_shift=blk.norm1.shift, eps=blk.norm1.eps, keep_sum=True)
+            branch = att(None, cache, pos, qkv=qkv)
+            x, h = linear_small(branch, fc.weight, fc.bias, gelu=True, resid=x, ln_scale=blk.norm2.scale,
+                                ln_shift=blk.norm2.shift, eps=blk.norm2.eps, keep_sum=True)
+            branch = linear_small(h, proj.weight, proj.bias)
+        fn = self.final_norm
+        if branch is None:
+            return linear_small(x, self.out_head.weight, ln_scale=fn.scale, ln_shift=fn.shift, eps=fn.eps)
+        return linear_small(branch, self.out_head.weight, resid=x, ln_scale=fn.scale, ln_shift=fn.shift, eps=fn.eps)
+
     @torch.no_grad()
     def capture_prefill(self, batch, n, last_token_only=False, warmup=3):
         """Record one prefill forward for a fixed [batch, n] shape as a CUDA graph and return
@@ -379,7 +419,10 @@ class GPTModel(nn.Module):
             x = self.tok_emb(in_idx) + self.pos_emb(torch.arange(pos, pos + n, device=in_idx.device))
         x = self.drop_emb(x)
         if self._fused_blocks and not self.training and x.dtype == torch.bfloat16:
-            x = self._blocks_fused(x.contiguous(), kv_caches, pos, last_token_only)
+            x = x.contiguous()
+            if _few_rows(x, True):
+                return self._blocks_one_row(x, kv_caches, pos)      # logits
+            x = self._blocks_fused(x, kv_caches, pos, last_token_only)
         else:
             if kv_caches is None:
                 x = self.trf_blocks(x)
