@@ -246,6 +246,38 @@ def time_add_layernorm(rows, cols, steps, warmup):
             "kernel": "fa::fa_add_layernorm_kernel"}
 
 
+def time_linear_small(M, N, K, steps, warmup):
+    """y = x W^T + b for M rows, one pass over W (N * K * 2 algorithmic bytes per launch).  Enough
+    different weight matrices are rotated that no launch finds its weights in L2."""
+    from tfg_flashattention_b200.block_ops import linear_small
+    g = torch.Generator(device="cuda").manual_seed(17)
+    n_sets = max(2, min(32, -(-300_000_000 // (N * K * 2))))
+    ws = [(torch.randn(N, K, device="cuda", generator=g) / K ** 0.5).bfloat16() for _ in range(n_sets)]
+    b = torch.randn(N, device="cuda", generator=g).bfloat16()
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    y = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    for i in range(max(warmup, 3)):
+        linear_small(x, ws[i % n_sets], b, out=y)
+    torch.cuda.synchronize()
+    # the kernel lives inside CUDA graphs in generation (a launch from Python costs more than the
+    # kernel runs): record `steps` launches as one graph and time its replay
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(steps):
+            linear_small(x, ws[i % n_sets], b, out=y)
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    return {"M": M, "N": N, "K": K, "us_per_launch": round(ms * 1e3, 2),
+            "gbs": round(N * K * 2 / (ms * 1e-3) / 1e9, 1), "weight_sets_rotated": n_sets,
+            "timing": "one CUDA-graph replay of all launches", "kernel": "fa::fa_linear_small_kernel"}
+
+
 def cpu_attention_sample(w, reps, threads):
     """Time the CPU oracle on CPU_SAMPLE_BATCH batch entries of workload w.  Returns TFLOP/s."""
     from oracle.attention_oracle import manual_attention
@@ -319,6 +351,8 @@ def main():
                     help="time only this decode step (small runs for profilers); prints a short line")
     ap.add_argument("--ln-case", default=None, metavar="rows,cols",
                     help="time only the residual add + LayerNorm kernel on this shape (for profiling)")
+    ap.add_argument("--linear-case", default=None, metavar="M,N,K",
+                    help="time only the few-rows Linear kernel on this shape (for profiling)")
     ap.add_argument("--case", default=None, metavar="B,H,N,causal",
                     help="time only this attention problem (small runs for profilers); prints a short line")
     args = ap.parse_args()
@@ -362,6 +396,11 @@ def main():
     if args.ln_case:
         lr, lc = (int(x) for x in args.ln_case.split(","))
         print(json.dumps({"ln_case": args.ln_case, **time_add_layernorm(lr, lc, args.steps, args.warmup)}), flush=True)
+        return
+
+    if args.linear_case:
+        lm, ln_, lk = (int(x) for x in args.linear_case.split(","))
+        print(json.dumps({"linear_case": args.linear_case, **time_linear_small(lm, ln_, lk, args.steps, args.warmup)}), flush=True)
         return
 
     if args.case:
@@ -516,6 +555,14 @@ def main():
             r["frac_of_hbm_peak"] = round(r["gbs"] / peaks["hbm_gbs"], 3)
             add_ln.append(r)
 
+    # ---------------------------------------------------------------- Linear for one row (generation)
+    lin = []
+    if not args.no_sweep:
+        for M, N, K in ((1, 4800, 1600), (1, 1600, 6400), (1, 50257, 1600)):   # GPT-2 XL: QKV, MLP-proj, head
+            r = time_linear_small(M, N, K, 100, 10)
+            r["frac_of_hbm_peak"] = round(r["gbs"] / peaks["hbm_gbs"], 3)
+            lin.append(r)
+
     # ---------------------------------------------------------------- the reference's own benchmark
     # "time for 20 tokens" (model_inference.py:444-465): B=1, a ~70-token prompt, 20 new tokens,
     # here with random-init weights and random token ids; with the K/V cache + decode kernel, and
@@ -580,7 +627,7 @@ def main():
             "gpu_launches": args.steps,
             "clocks": clocks,
             "cpu_baseline": cpu,
-            "extra": {"sweep": sweep, "gpt2_prefill": prefill, "decode_step": decode, "add_layernorm": add_ln,
+            "extra": {"sweep": sweep, "gpt2_prefill": prefill, "decode_step": decode, "add_layernorm": add_ln, "linear_small": lin,
                       "generate_20_tokens": gen},
         }
         print(json.dumps(line), flush=True)
