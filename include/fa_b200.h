@@ -110,8 +110,9 @@ int fa_b200_last_status(int device, void* stream);
  *
  * q and o are bf16 [B, H, 64] (strides {batch, head} in elements, multiples of 8); the caches are
  * bf16 [B, H, >= kv_len, 64] with strides {batch, head, row}; lse (optional) is fp32 [B, H].
- * With few (batch, head) pairs the keys of a head are processed in several chunks whose partial
- * results pass through `workspace`: device memory of at least
+ * With few (batch, head) pairs and a long cache the keys of a head are processed in several chunks
+ * whose partial results pass through `workspace` (few pairs with at most 4096 rows run as one
+ * wide CTA per head and need none): device memory of at least
  * fa_b200_decode_workspace_bytes(B, H, kv_len) bytes, 16-byte aligned, owned by the caller and not
  * shared by calls that may overlap on the GPU (it may be NULL when that function returns 0).
  */

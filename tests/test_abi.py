@@ -87,24 +87,26 @@ def test_strerror_covers_codes(fa_lib):
 def test_decode_workspace_query_and_validation(fa_lib):
     ws = fa_lib.fa_b200_decode_workspace_bytes
     assert ws(32, 25, 1024) == 0                       # 800 heads fill the GPU: keys are not split
-    assert ws(1, 25, 1024) == 25 * 16 * 66 * 4         # 25 heads: 16 chunks of 64 rows
-    assert ws(1, 1, 100) == 1 * 2 * 66 * 4
+    assert ws(1, 25, 1024) == 0                        # few heads, short cache: one wide CTA per head
+    assert ws(1, 25, 8192) == 25 * 24 * 66 * 4         # long cache: 24 chunks per head
+    assert ws(12, 25, 300) == 300 * 2 * 66 * 4         # 300 heads are too many for the wide form
+    assert ws(1, 1, 100) == 0
     assert ws(1, 1, 64) == 0
     assert ws(0, 5, 10) == 0
     assert ws(1, 1, 0) == -3 and ws(-1, 1, 5) == -3
     p = _lib.FaDecodeParams()
     p.q, p.k_cache, p.v_cache, p.o = 0x1000, 0x2000, 0x3000, 0x4000
-    p.B, p.H, p.kv_len, p.d = 1, 25, 1024, 64
+    p.B, p.H, p.kv_len, p.d = 1, 25, 8192, 64
     p.q_strides = p.o_strides = (ctypes.c_int64 * 2)(1600, 64)
-    p.k_strides = p.v_strides = (ctypes.c_int64 * 3)(25 * 1024 * 64, 1024 * 64, 64)
+    p.k_strides = p.v_strides = (ctypes.c_int64 * 3)(25 * 8192 * 64, 8192 * 64, 64)
     p.device = 0
     assert fa_lib.fa_b200_decode(ctypes.byref(p)) == -12     # needs a workspace, none given
     p.d = 128
     assert fa_lib.fa_b200_decode(ctypes.byref(p)) == -2
     p.d, p.kv_len = 64, 0
     assert fa_lib.fa_b200_decode(ctypes.byref(p)) == -3
-    p.kv_len = 1024
-    p.k_strides = (ctypes.c_int64 * 3)(25 * 1024 * 64, 1024 * 64, 60)
+    p.kv_len = 8192
+    p.k_strides = (ctypes.c_int64 * 3)(25 * 8192 * 64, 8192 * 64, 60)
     assert fa_lib.fa_b200_decode(ctypes.byref(p)) == -4
     assert fa_lib.fa_b200_decode(None) == -1
 

@@ -305,7 +305,8 @@ def _decode_oracle(q, k, v, kv_len, scale=None):
 
 
 @pytest.mark.parametrize("B,H,kv_len", [(1, 1, 1), (1, 2, 7), (2, 3, 64), (1, 25, 1000), (3, 5, 129),
-                                        (32, 25, 1024), (1, 12, 4096), (2, 1, 33)])
+                                        (32, 25, 1024), (1, 12, 4096), (2, 1, 33),      # one launch
+                                        (1, 25, 6000), (2, 3, 5000), (12, 25, 300)])    # split + combine
 def test_decode_parity(cfa, B, H, kv_len):
     """Single-query attention over a KV cache (split over chunks or not) against the oracle."""
     torch.manual_seed(B * 1000 + H * 10 + kv_len)

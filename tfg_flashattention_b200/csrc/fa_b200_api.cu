@@ -237,10 +237,21 @@ namespace {
 
 constexpr int kDecodeTargetCtas = 592;   // 4 CTAs per SM on a 148-SM part: enough loads in flight
 
+constexpr int kDecodeWideMaxHeads = 296;   // two 1024-thread CTAs per SM on a 148-SM part
+constexpr int kDecodeWideMaxLen = 4096;    // up to 1 MB of K/V per head through one SM
+
 // How the keys of one head are cut: `splits` chunks of `rows` rows (a multiple of the 16 lane
-// groups of a CTA).  The same rule sizes the workspace and launches the kernel.
-void decode_split(int B, int H, int kv_len, int* splits, int* rows) {
+// groups of a CTA).  The same rule sizes the workspace and launches the kernel.  Few heads with
+// short caches take the one-launch form instead (`wide`: one 1024-thread CTA per head, no split).
+void decode_split(int B, int H, int kv_len, int* splits, int* rows, bool* wide = nullptr) {
   const long long heads = static_cast<long long>(B) * H;
+  const bool w = heads <= kDecodeWideMaxHeads && kv_len <= kDecodeWideMaxLen;
+  if (wide != nullptr) *wide = w;
+  if (w) {
+    *splits = 1;
+    *rows = (kv_len + 127) / 128 * 128;
+    return;
+  }
   long long want = (kDecodeTargetCtas + heads - 1) / heads;
   const long long max_splits = (kv_len + 63) / 64;            // at least 64 rows per chunk
   if (want > max_splits) want = max_splits;
@@ -300,7 +311,8 @@ int fa_b200_decode(const fa_b200_decode_params* p) {
   if (rc != FA_B200_OK) return rc;
   if (p->B == 0 || p->H == 0) return FA_B200_OK;
   int splits = 1, rows = 0;
-  decode_split(p->B, p->H, p->kv_len, &splits, &rows);
+  bool wide = false;
+  decode_split(p->B, p->H, p->kv_len, &splits, &rows, &wide);
   if (splits > 1) {
     const int64_t need = fa_b200_decode_workspace_bytes(p->B, p->H, p->kv_len);
     if (p->workspace == nullptr || p->workspace_bytes < need ||
@@ -336,7 +348,8 @@ int fa_b200_decode(const fa_b200_decode_params* p) {
 
   const cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
   const dim3 grid(static_cast<unsigned>(p->B * p->H), static_cast<unsigned>(splits));
-  fa::fa_decode_partial_kernel<<<grid, fa::kDecodeThreads, 0, stream>>>(kp);
+  if (wide) fa::fa_decode_partial_kernel<fa::kDecodeWideThreads><<<grid, fa::kDecodeWideThreads, 0, stream>>>(kp);
+  else fa::fa_decode_partial_kernel<fa::kDecodeThreads><<<grid, fa::kDecodeThreads, 0, stream>>>(kp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
   if (splits > 1) {
@@ -377,7 +390,8 @@ int fa_b200_decode_static(const fa_b200_decode_params* p) {
   if (rc != FA_B200_OK) return rc;
   if (p->B == 0 || p->H == 0) return FA_B200_OK;
   int splits = 1, rows = 0;
-  decode_split(p->B, p->H, p->kv_len, &splits, &rows);
+  bool wide = false;
+  decode_split(p->B, p->H, p->kv_len, &splits, &rows, &wide);
   if (splits > 1 &&
       fa_b200_decode_workspace_bytes(p->B, p->H, p->kv_len) > static_cast<int64_t>(FA_B200_STATIC_SCRATCH_BYTES))
     return FA_B200_ERR_STATIC_SCRATCH;
@@ -414,7 +428,8 @@ int fa_b200_decode_static(const fa_b200_decode_params* p) {
 
   const cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
   const dim3 grid(static_cast<unsigned>(p->B * p->H), static_cast<unsigned>(splits));
-  fa::fa_decode_partial_kernel<<<grid, fa::kDecodeThreads, 0, stream>>>(kp);
+  if (wide) fa::fa_decode_partial_kernel<fa::kDecodeWideThreads><<<grid, fa::kDecodeWideThreads, 0, stream>>>(kp);
+  else fa::fa_decode_partial_kernel<fa::kDecodeThreads><<<grid, fa::kDecodeThreads, 0, stream>>>(kp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
   if (splits > 1) {

@@ -28,6 +28,7 @@ namespace fa {
 #endif
 constexpr int kDecodeThreads = FA_DECODE_THREADS;   // a warp's 32 lanes = 4 groups of 8 lanes
 constexpr int kDecodeGroups = kDecodeThreads / 8;   // 16 lane groups, each owns whole rows
+constexpr int kDecodeWideThreads = 1024;            // the one-CTA-per-head form for few heads
 constexpr int kDecodeUnroll = FA_DECODE_UNROLL;     // rows in flight per lane group
 constexpr int kDecodePartial = 66;           // floats per partial: m, l, o[64]
 
@@ -67,9 +68,17 @@ __device__ __forceinline__ void bf16x8_to_float(const uint4& raw, float (&f)[8])
   }
 }
 
-// grid (B*H, splits), block 128.  Lane group g = tid / 8 owns rows g, g+16, g+32, ... of the
-// chunk; lane c = tid % 8 owns columns 8c .. 8c+7 of every row.
-__global__ void __launch_bounds__(kDecodeThreads) fa_decode_partial_kernel(const DecodeParams p) {
+// grid (B*H, splits), block kThreads.  Lane group g = tid / 8 owns rows g, g + kGroups, ... of the
+// chunk; lane c = tid % 8 owns columns 8c .. 8c+7 of every row.  kThreads = 128 is the split-KV
+// form; kThreads = 1024 (always with splits == 1) serves problems with few (batch, head) pairs and
+// short caches in ONE launch: a head's keys stream through one SM (a few hundred KB), and the
+// 128 lane groups are merged inside the CTA, with no scratch buffer and no second kernel -- at
+// batch 1 the two launches of the split form cost more than the attention itself.
+template <int kThreads>
+__global__ void __launch_bounds__(kThreads) fa_decode_partial_kernel(const DecodeParams p) {
+  constexpr int kGroups = kThreads / 8;
+  // rows in flight per lane group: the wide form has 64 registers per thread and 8x the threads
+  constexpr int kUnroll = kThreads > 256 ? 2 : kDecodeUnroll;
   const int bh = blockIdx.x;
   const int split = blockIdx.y;
   const int b = bh / p.H;
@@ -100,12 +109,12 @@ __global__ void __launch_bounds__(kDecodeThreads) fa_decode_partial_kernel(const
 
   // The loop bounds are the same for every thread of the CTA (the shuffles below name the whole
   // warp); which rows exist is decided per lane group inside.
-  for (int base = row_begin; base < row_end; base += kDecodeGroups * kDecodeUnroll) {
+  for (int base = row_begin; base < row_end; base += kGroups * kUnroll) {
     const int r0 = base + g;
-    uint4 kraw[kDecodeUnroll], vraw[kDecodeUnroll];
+    uint4 kraw[kUnroll], vraw[kUnroll];
 #pragma unroll
-    for (int u = 0; u < kDecodeUnroll; ++u) {           // all loads first: rows in flight
-      const int r = r0 + u * kDecodeGroups;
+    for (int u = 0; u < kUnroll; ++u) {           // all loads first: rows in flight
+      const int r = r0 + u * kGroups;
       if (r < row_end) {
         const bool fresh = knew != nullptr && r == kv_len - 1;   // the row being appended
         kraw[u] = *reinterpret_cast<const uint4*>(fresh ? knew : kbase + (long long)r * p.k_sn);
@@ -117,8 +126,8 @@ __global__ void __launch_bounds__(kDecodeThreads) fa_decode_partial_kernel(const
       }
     }
 #pragma unroll
-    for (int u = 0; u < kDecodeUnroll; ++u) {
-      const int r = r0 + u * kDecodeGroups;
+    for (int u = 0; u < kUnroll; ++u) {
+      const int r = r0 + u * kGroups;
       // the 8 lanes of a group must all run the shuffles; rows past the end contribute nothing
       float kf[8], s = 0.f;
       if (r < row_end) {
@@ -143,21 +152,42 @@ __global__ void __launch_bounds__(kDecodeThreads) fa_decode_partial_kernel(const
     }
   }
 
-  // ---- merge the 16 lane groups of the CTA: (m, l, acc) per group, columns stay with lane c
-  __shared__ float sm_m[kDecodeGroups], sm_l[kDecodeGroups];
-  __shared__ float sm_o[kDecodeGroups][64];
-  if (c == 0) { sm_m[g] = m; sm_l[g] = l; }
+  // ---- merge the lane groups of the CTA: (m, l, acc) per group, columns stay with lane c.
+  // The wide form first folds the four groups of every warp with shuffles, so that shared memory
+  // and the final loop see one entry per warp (32) instead of one per group (128).
+  constexpr int kEntries = kThreads > 256 ? kThreads / 32 : kGroups;
+  if constexpr (kThreads > 256) {
 #pragma unroll
-  for (int i = 0; i < 8; ++i) sm_o[g][8 * c + i] = acc[i];
+    for (int off = 8; off <= 16; off <<= 1) {
+      const float m_o = __shfl_xor_sync(0xffffffffu, m, off);
+      const float l_o = __shfl_xor_sync(0xffffffffu, l, off);
+      const float m_n = fmaxf(m, m_o);
+      const float f_a = m == -CUDART_INF_F ? 0.f : exp2f(m - m_n);     // empty groups carry -inf
+      const float f_b = m_o == -CUDART_INF_F ? 0.f : exp2f(m_o - m_n);
+      l = l * f_a + l_o * f_b;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = acc[i] * f_a + __shfl_xor_sync(0xffffffffu, acc[i], off) * f_b;
+      m = m_n;
+    }
+  }
+  const int entry = kThreads > 256 ? tid >> 5 : g;
+  const bool writer = kThreads > 256 ? (tid & 31) < 8 : true;          // one group per warp writes
+  __shared__ float sm_m[kEntries], sm_l[kEntries];
+  __shared__ float sm_o[kEntries][64];
+  if (writer) {
+    if (c == 0) { sm_m[entry] = m; sm_l[entry] = l; }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sm_o[entry][8 * c + i] = acc[i];
+  }
   __syncthreads();
   if (tid < 64) {
     float mm = -CUDART_INF_F;
-#pragma unroll
-    for (int i = 0; i < kDecodeGroups; ++i) mm = fmaxf(mm, sm_m[i]);
+#pragma unroll 16
+    for (int i = 0; i < kEntries; ++i) mm = fmaxf(mm, sm_m[i]);
     float ll = 0.f, oo = 0.f;
-#pragma unroll
-    for (int i = 0; i < kDecodeGroups; ++i) {
-      const float f = sm_m[i] == -CUDART_INF_F ? 0.f : exp2f(sm_m[i] - mm);   // empty groups
+#pragma unroll 16
+    for (int i = 0; i < kEntries; ++i) {
+      const float f = sm_m[i] == -CUDART_INF_F ? 0.f : exp2f(sm_m[i] - mm);   // empty entries
       ll += sm_l[i] * f;
       oo += sm_o[i][tid] * f;
     }
