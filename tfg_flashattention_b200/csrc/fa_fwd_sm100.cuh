@@ -19,7 +19,10 @@
 //   warpgroup 0           softmax, one thread per query row.  Pulls its S row from TMEM into
 //                         registers and releases S at once, so the issuer can start S for the
 //                         next K tile while this one is exponentiated; keeps the running max and
-//                         sum; writes P (bf16) to its own TMEM columns; rescales O in TMEM only
+//                         sum (scaling and sums as packed f32x2 operations; 2 of every 8
+//                         exponentials as a cubic on the FMA pipe, the rest on the MUFU: d = 64
+//                         is exponential-bound before it is MMA-bound);
+//                         writes P (bf16) to its own TMEM columns; rescales O in TMEM only
 //                         when the running max grew by more than 2^8; epilogue: O / l -> bf16 ->
 //                         swizzled shared-memory tile -> TMA store, and the LSE.
 //
