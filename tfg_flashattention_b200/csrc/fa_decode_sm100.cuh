@@ -117,8 +117,9 @@ __global__ void __launch_bounds__(kThreads) fa_decode_partial_kernel(const Decod
       const int r = r0 + u * kGroups;
       if (r < row_end) {
         const bool fresh = knew != nullptr && r == kv_len - 1;   // the row being appended
-        kraw[u] = *reinterpret_cast<const uint4*>(fresh ? knew : kbase + (long long)r * p.k_sn);
-        vraw[u] = *reinterpret_cast<const uint4*>(fresh ? vnew : vbase + (long long)r * p.v_sn);
+        // streaming loads: every cache byte is read once per step
+        kraw[u] = __ldcs(reinterpret_cast<const uint4*>(fresh ? knew : kbase + (long long)r * p.k_sn));
+        vraw[u] = __ldcs(reinterpret_cast<const uint4*>(fresh ? vnew : vbase + (long long)r * p.v_sn));
         if (fresh) {
           *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(kbase) + (long long)r * p.k_sn) = kraw[u];
           *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(vbase) + (long long)r * p.v_sn) = vraw[u];
