@@ -74,8 +74,8 @@ __global__ void __launch_bounds__(kLnWarpsPerCta * 32) fa_add_layernorm_kernel(c
   for (int i = 0; i < kVecPerLane; ++i) {
     const int v = lane + 32 * i;
     if (v < nvec) {
-      a_raw[i] = a[v];
-      if (rs) r_raw[i] = rs[v];
+      a_raw[i] = __ldcs(a + v);      // streaming: each activation byte is read once
+      if (rs) r_raw[i] = __ldcs(rs + v);
     }
   }
   float x[kVecPerLane][8];

@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(kLinWarps * 32) fa_linear_small_kernel(const L
 #pragma unroll
       for (int u = 0; u < kLinUnroll; ++u) {         // all loads first
         const int v = v0 + 32 * u;
-        wv[u] = v < nvec ? __ldg(wrow + v) : make_uint4(0u, 0u, 0u, 0u);
+        wv[u] = v < nvec ? __ldcs(wrow + v) : make_uint4(0u, 0u, 0u, 0u);   // streaming: read once
       }
 #pragma unroll
       for (int u = 0; u < kLinUnroll; ++u) {
