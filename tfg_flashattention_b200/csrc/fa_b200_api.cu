@@ -541,8 +541,13 @@ int g_lin_error[kMaxDevices];
 
 template <int kRows>
 cudaError_t lin_prepare() {
-  return cudaFuncSetAttribute(reinterpret_cast<const void*>(&fa::fa_linear_small_kernel<kRows>),
-                              cudaFuncAttributeMaxDynamicSharedMemorySize, kLinSmemLimit);
+  cudaError_t e = cudaFuncSetAttribute(
+      reinterpret_cast<const void*>(&fa::fa_linear_small_kernel<kRows, fa::kLinUnrollShort>),
+      cudaFuncAttributeMaxDynamicSharedMemorySize, kLinSmemLimit);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(
+      reinterpret_cast<const void*>(&fa::fa_linear_small_kernel<kRows, fa::kLinUnrollLong>),
+      cudaFuncAttributeMaxDynamicSharedMemorySize, kLinSmemLimit);
 }
 void lin_init(int dev) {   // with `dev` current
   cudaError_t e = lin_prepare<1>();
@@ -559,7 +564,12 @@ cudaError_t lin_launch(const fa::LinearSmallParams& kp, cudaStream_t stream, int
   per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
   long long ctas = (kp.N + fa::kLinWarps - 1) / fa::kLinWarps;
   if (ctas > per_sm * sm_count) ctas = per_sm * sm_count;
-  fa::fa_linear_small_kernel<kRows><<<static_cast<unsigned>(ctas), fa::kLinWarps * 32, smem, stream>>>(kp);
+  // more loads in flight per lane pay for long rows and for many columns per warp (measured:
+  // the vocabulary head 31 -> 28 us, K = 6400 9.2 -> 8.2 us; the short layers are better with 4)
+  if (kp.K > 2048 || kp.N >= 16384)
+    fa::fa_linear_small_kernel<kRows, fa::kLinUnrollLong><<<static_cast<unsigned>(ctas), fa::kLinWarps * 32, smem, stream>>>(kp);
+  else
+    fa::fa_linear_small_kernel<kRows, fa::kLinUnrollShort><<<static_cast<unsigned>(ctas), fa::kLinWarps * 32, smem, stream>>>(kp);
   return cudaGetLastError();
 }
 

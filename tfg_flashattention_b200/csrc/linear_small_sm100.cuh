@@ -30,7 +30,8 @@ namespace fa {
 
 constexpr int kLinWarps = 8;            // output columns per CTA
 constexpr int kLinMaxRows = 8;          // rows of x
-constexpr int kLinUnroll = 4;           // 16-byte weight loads in flight per lane
+constexpr int kLinUnrollShort = 4;      // 16-byte weight loads in flight per lane: short rows ...
+constexpr int kLinUnrollLong = 8;       // ... and rows of K > 2048 or very many columns (measured)
 
 struct LinearSmallParams {
   const __nv_bfloat16* x;      // [M, K]
@@ -54,7 +55,7 @@ __device__ __forceinline__ float gelu_tanh(float v) {
   return 0.5f * v * (1.0f + tanhf(u));
 }
 
-template <int kRows>
+template <int kRows, int kLinUnroll>
 __global__ void __launch_bounds__(kLinWarps * 32) fa_linear_small_kernel(const LinearSmallParams p) {
   extern __shared__ uint4 lin_smem[];              // x: kRows rows of K/8 16-byte vectors
   const int nvec = p.K >> 3;
