@@ -35,7 +35,7 @@
 extern "C" {
 #endif
 
-#define FA_B200_ABI_VERSION 3
+#define FA_B200_ABI_VERSION 4
 
 /* argument errors (negative return values) */
 #define FA_B200_OK                 0
@@ -76,6 +76,24 @@ typedef struct fa_b200_params {
  * launched, like the reference launcher (v1.cu:29-37).  Replaces flashattention_forward<T>
  * (reference src/cpp/v1.cu:4-38). */
 int fa_b200_fwd(const fa_b200_params* p);
+
+/* How fa_b200_fwd would schedule this problem on p->device, without launching anything.  The
+ * reference launcher has one fixed shape, a CTA per 32-row tile (grid (ceil(N/32), H, B),
+ * src/cpp/v1.cu:13-14, 25-34); this library picks one of four kernel schedules per call and this
+ * query reports the pick, so that a test or a tuning run can tell which code ran:
+ *   FA_B200_SCHEDULE_CTA_PER_TILE        one CTA per 128-row query tile, heaviest causal tile first
+ *   FA_B200_SCHEDULE_PERSISTENT_PAIRED   resident CTAs, causal, complementary tile pairs
+ *   FA_B200_SCHEDULE_PERSISTENT_ROTATED  resident CTAs, causal, odd tile count (rotated order)
+ *   FA_B200_SCHEDULE_PERSISTENT_FULL     resident CTAs, non-causal
+ *   FA_B200_SCHEDULE_NONE                empty problem, nothing is launched
+ * *grid receives the number of CTAs.  Either output pointer may be NULL.  Arguments are checked as
+ * by fa_b200_fwd; the first call on a device performs the same one-time device set-up. */
+#define FA_B200_SCHEDULE_NONE               -1
+#define FA_B200_SCHEDULE_CTA_PER_TILE        0
+#define FA_B200_SCHEDULE_PERSISTENT_PAIRED   1
+#define FA_B200_SCHEDULE_PERSISTENT_ROTATED  2
+#define FA_B200_SCHEDULE_PERSISTENT_FULL     3
+int fa_b200_fwd_plan(const fa_b200_params* p, int32_t* schedule, int32_t* grid);
 
 /* Check arguments exactly as fa_b200_fwd does, without touching CUDA.  Returns 0 or a negative
  * FA_B200_ERR_* code.  Covers what CHECK_INPUT and the dtype branch police in the reference

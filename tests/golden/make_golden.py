@@ -18,7 +18,11 @@ Fixtures written (all float32 / int64 numpy arrays):
                          `attn_weights @ values` (:75) recovered from the tensor it feeds out_proj.
   gpt_tiny.npz           a 2-layer GPTModel (emb 128, 2 heads of 64, vocab 97, ctx 48, qkv_bias
                          as the reference driver sets it, :422): every state_dict entry, the token
-                         ids, and the logits.
+                         (the `att.mask` buffers included), the token ids, and the logits.
+  loader_tiny.npz        a synthetic parameter dictionary in the OpenAI checkpoint layout
+                         (`p.<path>` entries: wte, wpe, g, b, blocks.<i>.attn.c_attn.w ...) and the
+                         state_dict (`sd.<name>`) of a reference GPTModel after the reference's own
+                         load_weights_into_gpt(gpt, params) (model_inference.py:313-376) ran on it.
 """
 import sys
 import types
@@ -83,12 +87,50 @@ def gpt_tiny(mi):
     with torch.no_grad(), warnings.catch_warnings():
         warnings.simplefilter("ignore")   # autocast("cuda") warns on a CPU-only box and is inert
         logits = gpt(ids)
-    out = {f"sd.{k}": v.detach().numpy() for k, v in gpt.state_dict().items()
-           if not k.endswith(".mask")}
+    out = {f"sd.{k}": v.detach().numpy() for k, v in gpt.state_dict().items()}   # unmodified, `att.mask` included
     out["ids"] = ids.numpy()
     out["logits"] = logits.numpy()
     out["n_layers"] = np.array(cfg["n_layers"])
     out["n_heads"] = np.array(cfg["n_heads"])
+    return out
+
+
+LOADER_CFG = {"vocab_size": 31, "context_length": 8, "emb_dim": 32, "n_heads": 2, "n_layers": 2,
+              "drop_rate": 0.0, "qkv_bias": True, "impl_type": "manual"}
+
+
+def openai_params(cfg, seed):
+    """A parameter dictionary in the checkpoint's own layout ([in, out] weights, fused c_attn)."""
+    rng = np.random.default_rng(seed)
+    d, v, ctx = cfg["emb_dim"], cfg["vocab_size"], cfg["context_length"]
+    f = lambda *shape: rng.normal(0.0, 0.05, shape).astype(np.float32)
+    blocks = [{"attn": {"c_attn": {"w": f(d, 3 * d), "b": f(3 * d)}, "c_proj": {"w": f(d, d), "b": f(d)}},
+               "mlp": {"c_fc": {"w": f(d, 4 * d), "b": f(4 * d)}, "c_proj": {"w": f(4 * d, d), "b": f(d)}},
+               "ln_1": {"g": 1 + f(d), "b": f(d)}, "ln_2": {"g": 1 + f(d), "b": f(d)}}
+              for _ in range(cfg["n_layers"])]
+    return {"wte": f(v, d), "wpe": f(ctx, d), "g": 1 + f(d), "b": f(d), "blocks": blocks}
+
+
+def _flatten(prefix, node, out):
+    if isinstance(node, dict):
+        for k, v in node.items():
+            _flatten(f"{prefix}.{k}" if prefix else k, v, out)
+    elif isinstance(node, list):
+        for i, v in enumerate(node):
+            _flatten(f"{prefix}.{i}", v, out)
+    else:
+        out[prefix] = node
+
+
+def loader_tiny(mi):
+    params = openai_params(LOADER_CFG, 5)
+    torch.manual_seed(9)
+    gpt = mi.GPTModel(LOADER_CFG).eval()
+    mi.load_weights_into_gpt(gpt, params)           # the reference's loader, unmodified
+    flat = {}
+    _flatten("", params, flat)
+    out = {f"p.{k}": v for k, v in flat.items()}
+    out.update({f"sd.{k}": v.detach().numpy() for k, v in gpt.state_dict().items()})
     return out
 
 
@@ -100,4 +142,5 @@ if __name__ == "__main__":
     mi = import_reference(ref_root)
     np.savez_compressed(f"{here}/attn_manual_cases.npz", **attention_cases(mi))
     np.savez_compressed(f"{here}/gpt_tiny.npz", **gpt_tiny(mi))
-    print("wrote", f"{here}/attn_manual_cases.npz", f"{here}/gpt_tiny.npz")
+    np.savez_compressed(f"{here}/loader_tiny.npz", **loader_tiny(mi))
+    print("wrote", f"{here}/attn_manual_cases.npz", f"{here}/gpt_tiny.npz", f"{here}/loader_tiny.npz")

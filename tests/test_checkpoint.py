@@ -82,3 +82,27 @@ def test_loading_drops_stale_inference_caches():
     checkpoint.load_weights_into_gpt(fresh, _openai_params(5))
     with torch.no_grad():
         torch.testing.assert_close(model(ids), fresh(ids))
+
+
+def test_same_state_dict_as_the_reference_loader(golden_dir, tmp_path):
+    """tests/golden/loader_tiny.npz holds a parameter dictionary and the state_dict the
+    reference's own load_weights_into_gpt (model_inference.py:313-376) made of it; this loader
+    must produce the same state_dict bit for bit -- and the reference's dict, `att.mask` buffers
+    included, must load into the harness model with strict=True."""
+    t = np.load(os.path.join(golden_dir, "loader_tiny.npz"))
+    cfg = {"vocab_size": 31, "context_length": 8, "emb_dim": 32, "n_heads": 2, "n_layers": 2,
+           "drop_rate": 0.0, "qkv_bias": True, "impl_type": "manual"}
+    flat = os.path.join(tmp_path, "flat.npz")
+    np.savez(flat, **{k[2:]: t[k] for k in t.files if k.startswith("p.")})
+    params = checkpoint.load_params_npz(flat)
+    model = gpt2.GPTModel(cfg).eval()
+    checkpoint.load_weights_into_gpt(model, params)
+    ref_sd = {k[3:]: torch.from_numpy(t[k]) for k in t.files if k.startswith("sd.")}
+    ours = model.state_dict()
+    assert sorted(ours.keys()) == sorted(ref_sd.keys())          # incl. trf_blocks.N.att.mask
+    for k, v in ref_sd.items():
+        assert torch.equal(ours[k], v), k
+    other = gpt2.GPTModel(cfg).eval()
+    other.load_state_dict(ref_sd, strict=True)
+    for k, v in ref_sd.items():
+        assert torch.equal(other.state_dict()[k], v), k

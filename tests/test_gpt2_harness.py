@@ -13,8 +13,11 @@ def _load_tiny(golden_dir, impl):
     cfg = {"vocab_size": 97, "context_length": 48, "emb_dim": 128, "n_heads": int(t["n_heads"]),
            "n_layers": int(t["n_layers"]), "drop_rate": 0.0, "qkv_bias": True, "impl_type": impl}
     model = gpt2.GPTModel(cfg).eval()
+    # the reference's state_dict exactly as it saved it, `att.mask` buffers included
     sd = {k[3:]: torch.from_numpy(t[k]) for k in t.files if k.startswith("sd.")}
-    missing, unexpected = model.load_state_dict(sd, strict=True)
+    assert any(k.endswith(".att.mask") for k in sd)
+    model.load_state_dict(sd, strict=True)
+    assert sorted(model.state_dict().keys()) == sorted(sd.keys())
     return model, torch.from_numpy(t["ids"]), torch.from_numpy(t["logits"])
 
 

@@ -10,7 +10,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libfa_b200.so")
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 
 class FaParams(ctypes.Structure):
@@ -62,9 +62,12 @@ class FaLinearSmallParams(ctypes.Structure):
     ]
 
 
-EXPORTS = ("fa_b200_fwd", "fa_b200_validate", "fa_b200_strerror", "fa_b200_device_ok",
+EXPORTS = ("fa_b200_fwd", "fa_b200_fwd_plan", "fa_b200_validate", "fa_b200_strerror", "fa_b200_device_ok",
            "fa_b200_last_status", "fa_b200_abi_version", "fa_b200_decode", "fa_b200_decode_workspace_bytes", "fa_b200_decode_static",
            "fa_b200_add_layernorm", "fa_b200_linear_small")
+
+SCHEDULES = {-1: "none", 0: "cta_per_tile", 1: "persistent_paired", 2: "persistent_rotated",
+             3: "persistent_full"}
 
 _lib = None
 
@@ -79,9 +82,15 @@ def load() -> ctypes.CDLL:
             f"{LIB_PATH} is missing: build it with `python -m tfg_flashattention_b200.build` "
             "(needs nvcc; there is no CPU or PyTorch fallback for this kernel)")
     lib = ctypes.CDLL(LIB_PATH)
+    missing = [name for name in EXPORTS if not hasattr(lib, name)]
+    if missing:
+        raise RuntimeError(f"{LIB_PATH} lacks {', '.join(missing)}: it was built from older sources; "
+                           "rebuild it with `python -m tfg_flashattention_b200.build --force`")
     P = ctypes.POINTER(FaParams)
     lib.fa_b200_fwd.argtypes = [P]
     lib.fa_b200_fwd.restype = ctypes.c_int
+    lib.fa_b200_fwd_plan.argtypes = [P, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_int32)]
+    lib.fa_b200_fwd_plan.restype = ctypes.c_int
     lib.fa_b200_validate.argtypes = [P]
     lib.fa_b200_validate.restype = ctypes.c_int
     lib.fa_b200_strerror.argtypes = [ctypes.c_int]

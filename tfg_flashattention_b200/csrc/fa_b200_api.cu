@@ -120,8 +120,8 @@ bool stride_ok(const int64_t s[3]) {
   return true;
 }
 
-int encode_map(CUtensorMap* map, const void* base, const fa_b200_params* p, const int64_t st[3],
-               unsigned box_rows = fa::kBlockN) {
+int encode_map_uncached(CUtensorMap* map, const void* base, const fa_b200_params* p,
+                        const int64_t st[3], unsigned box_rows) {
   // dims, innermost first: d, N, H, B.  Strides (bytes) for dims 1..3: row, head, batch.
   const cuuint64_t dims[4] = {static_cast<cuuint64_t>(p->d), static_cast<cuuint64_t>(p->N),
                               static_cast<cuuint64_t>(p->H), static_cast<cuuint64_t>(p->B)};
@@ -134,6 +134,87 @@ int encode_map(CUtensorMap* map, const void* base, const fa_b200_params* p, cons
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : FA_B200_ERR_TENSORMAP;
+}
+
+// A tensor map is a pure function of (base, shape, strides, box): the driver call that encodes
+// one costs about a microsecond, four of them per launch are a visible share of a small problem's
+// launch path, and callers (a model's layers, a benchmark loop) present the same few buffers
+// again and again.  Each host thread keeps a small direct-mapped cache of encoded maps; a hit
+// needs no lock and can never be stale, because nothing outside the key enters the encoding.
+struct MapKey {
+  const void* base;
+  int32_t B, H, N, box_rows;
+  int64_t st[3];
+  bool operator==(const MapKey& o) const {
+    return base == o.base && B == o.B && H == o.H && N == o.N && box_rows == o.box_rows &&
+           st[0] == o.st[0] && st[1] == o.st[1] && st[2] == o.st[2];
+  }
+};
+struct MapSlot {
+  MapKey key;
+  bool valid = false;
+  alignas(64) CUtensorMap map;
+};
+constexpr int kMapCacheSlots = 64;
+
+int encode_map(CUtensorMap* map, const void* base, const fa_b200_params* p, const int64_t st[3],
+               unsigned box_rows = fa::kBlockN) {
+  static thread_local MapSlot cache[kMapCacheSlots];
+  const MapKey key{base, p->B, p->H, p->N, static_cast<int32_t>(box_rows), {st[0], st[1], st[2]}};
+  uint64_t h = reinterpret_cast<uintptr_t>(base) >> 4;
+  h ^= (static_cast<uint64_t>(p->N) * 0x9E3779B97F4A7C15ull) ^ (static_cast<uint64_t>(st[2]) << 17) ^
+       (static_cast<uint64_t>(box_rows) << 7) ^ (static_cast<uint64_t>(p->B) << 40) ^
+       (static_cast<uint64_t>(p->H) << 52);
+  h ^= h >> 29;
+  MapSlot& slot = cache[(h * 0xBF58476D1CE4E5B9ull) >> 58];
+  if (slot.valid && slot.key == key) {
+    *map = slot.map;
+    return 0;
+  }
+  const int rc = encode_map_uncached(&slot.map, base, p, st, box_rows);
+  slot.valid = rc == 0;
+  if (rc != 0) return rc;
+  slot.key = key;
+  *map = slot.map;
+  return 0;
+}
+
+// How one forward call is scheduled (the rule behind fa_b200_fwd and fa_b200_fwd_plan).
+struct FwdPlan {
+  bool persistent;     // grid of resident CTAs striding through the work list
+  bool paired;         // persistent causal schedule of complementary tile pairs
+  int n_qtiles;
+  long long items;     // B * H * n_qtiles
+  unsigned grid;
+};
+
+FwdPlan plan_fwd(const fa_b200_params* p, const DeviceState& st) {
+  FwdPlan pl;
+  pl.n_qtiles = (p->N + fa::kBlockM - 1) / fa::kBlockM;
+  pl.items = static_cast<long long>(p->B) * p->H * pl.n_qtiles;
+  const int kv_tiles = (p->N + fa::kBlockN - 1) / fa::kBlockN;
+  const bool causal = p->causal != 0;
+  // Measured on B200: the causal schedule of complementary tile pairs wins up to N = 2048 at any
+  // grid size (equal at 4096, behind beyond: long items amortise their own start-up, and the
+  // hardware's dynamic placement of many CTAs balances better); without pairing, persistence pays
+  // for short items (N <= 1024) once every CTA gets at least two of them.
+  const bool can_pair = causal && pl.n_qtiles % 2 == 0;
+  pl.persistent = can_pair ? kv_tiles <= 16
+                           : (pl.items >= 2LL * st.resident_ctas && kv_tiles <= 8);
+  pl.paired = pl.persistent && can_pair;
+  const long long work_units = pl.paired ? pl.items / 2 : pl.items;
+  pl.grid = static_cast<unsigned>(
+      pl.persistent ? (work_units > st.resident_ctas ? st.resident_ctas : work_units) : pl.items);
+  return pl;
+}
+
+// Device guard + per-device set-up shared by the forward entry points.
+int ready_device(int device, DeviceState** out) {
+  DeviceState& st = g_dev[device];
+  std::call_once(st.once, init_device, device);
+  if (st.init_error) return st.init_error;
+  *out = &st;
+  return 0;
 }
 
 }  // namespace
@@ -172,9 +253,9 @@ int fa_b200_fwd(const fa_b200_params* p) {
 
   DeviceGuard guard(p->device);
   if (guard.error) return guard.error;
-  DeviceState& st = g_dev[p->device];
-  std::call_once(st.once, init_device, p->device);
-  if (st.init_error) return st.init_error;
+  DeviceState* stp = nullptr;
+  if ((rc = ready_device(p->device, &stp)) != 0) return rc;
+  const DeviceState& st = *stp;
   std::call_once(g_encode_once, resolve_encode);
   if (g_encode == nullptr) return FA_B200_ERR_DRIVER;
 
@@ -184,52 +265,54 @@ int fa_b200_fwd(const fa_b200_params* p) {
   if ((rc = encode_map(&mv, p->v, p, p->v_strides)) != 0) return rc;
   if ((rc = encode_map(&mo, p->o, p, p->o_strides, 32)) != 0) return rc;   // one 32-row slab per warp
 
+  const FwdPlan pl = plan_fwd(p, st);
   fa::FwdParams kp;
   kp.lse = p->lse;
   kp.B = p->B;
   kp.H = p->H;
   kp.N = p->N;
-  kp.n_qtiles = (p->N + fa::kBlockM - 1) / fa::kBlockM;
+  kp.n_qtiles = pl.n_qtiles;
   kp.div_qtiles = fa::make_fast_div(static_cast<uint32_t>(kp.n_qtiles));
   kp.div_heads = fa::make_fast_div(static_cast<uint32_t>(p->H));
   kp.causal = p->causal ? 1 : 0;
   const float scale = p->softmax_scale > 0.0f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(p->d));
   kp.scale_log2 = scale * 1.4426950408889634f;
   kp.status = st.status;
-
-  const long long items = static_cast<long long>(p->B) * p->H * kp.n_qtiles;
-  kp.n_items = static_cast<int>(items);
-  // Persistent grid (2 CTAs per SM, each striding through the item list) when the items are
-  // many and short; otherwise one CTA per item, which the hardware balances dynamically.
-  // FA_B200_PERSISTENT=0/1 in the environment overrides the choice (for measurements).
-  static const int persistent_env = [] {
-    const char* e = std::getenv("FA_B200_PERSISTENT");
-    return e == nullptr ? -1 : (e[0] == '0' ? 0 : 1);
-  }();
-  const int kv_tiles = (p->N + fa::kBlockN - 1) / fa::kBlockN;
-  // Measured on B200: the causal schedule of complementary tile pairs wins up to N = 2048 at any
-  // grid size (equal at 4096, behind beyond: long items amortise their own start-up, and the
-  // hardware's dynamic placement of many CTAs balances better); without pairing, persistence pays
-  // for short items (N <= 1024) once every CTA gets at least two of them.
-  const bool can_pair = kp.causal && kp.n_qtiles % 2 == 0;
-  const bool auto_persistent = can_pair ? kv_tiles <= 16
-                                        : (items >= 2LL * st.resident_ctas && kv_tiles <= 8);
-  const bool persistent = persistent_env < 0 ? auto_persistent : persistent_env == 1;
-  kp.paired = (persistent && kp.causal && kp.n_qtiles % 2 == 0) ? 1 : 0;
-  kp.n_units = static_cast<int>(items / 2);
+  kp.n_items = static_cast<int>(pl.items);
+  kp.paired = pl.paired ? 1 : 0;
+  kp.n_units = static_cast<int>(pl.items / 2);
   kp.div_half = fa::make_fast_div(static_cast<uint32_t>(kp.n_qtiles > 1 ? kp.n_qtiles / 2 : 1));
   const cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
-  const long long work_units = kp.paired ? kp.n_units : items;
-  const unsigned grid = static_cast<unsigned>(
-      persistent ? (work_units > st.resident_ctas ? st.resident_ctas : work_units) : items);
-  if (persistent) {
-    if (kp.causal) fa::fa_fwd_kernel<true, true><<<grid, fa::kNumThreads, fa::kSmemBytes, stream>>>(mq, mk, mv, mo, kp);
-    else fa::fa_fwd_kernel<true, false><<<grid, fa::kNumThreads, fa::kSmemBytes, stream>>>(mq, mk, mv, mo, kp);
+  if (pl.persistent) {
+    if (kp.causal) fa::fa_fwd_kernel<true, true><<<pl.grid, fa::kNumThreads, fa::kSmemBytes, stream>>>(mq, mk, mv, mo, kp);
+    else fa::fa_fwd_kernel<true, false><<<pl.grid, fa::kNumThreads, fa::kSmemBytes, stream>>>(mq, mk, mv, mo, kp);
   } else {
-    if (kp.causal) fa::fa_fwd_kernel<false, true><<<grid, fa::kNumThreads, fa::kSmemBytes, stream>>>(mq, mk, mv, mo, kp);
-    else fa::fa_fwd_kernel<false, false><<<grid, fa::kNumThreads, fa::kSmemBytes, stream>>>(mq, mk, mv, mo, kp);
+    if (kp.causal) fa::fa_fwd_kernel<false, true><<<pl.grid, fa::kNumThreads, fa::kSmemBytes, stream>>>(mq, mk, mv, mo, kp);
+    else fa::fa_fwd_kernel<false, false><<<pl.grid, fa::kNumThreads, fa::kSmemBytes, stream>>>(mq, mk, mv, mo, kp);
   }
   return static_cast<int>(cudaGetLastError());
+}
+
+int fa_b200_fwd_plan(const fa_b200_params* p, int32_t* schedule, int32_t* grid) {
+  int rc = fa_b200_validate(p);
+  if (rc != FA_B200_OK) return rc;
+  if (p->B == 0 || p->H == 0 || p->N == 0) {
+    if (schedule != nullptr) *schedule = FA_B200_SCHEDULE_NONE;
+    if (grid != nullptr) *grid = 0;
+    return FA_B200_OK;
+  }
+  DeviceGuard guard(p->device);
+  if (guard.error) return guard.error;
+  DeviceState* stp = nullptr;
+  if ((rc = ready_device(p->device, &stp)) != 0) return rc;
+  const FwdPlan pl = plan_fwd(p, *stp);
+  if (schedule != nullptr)
+    *schedule = !pl.persistent ? FA_B200_SCHEDULE_CTA_PER_TILE
+                : pl.paired    ? FA_B200_SCHEDULE_PERSISTENT_PAIRED
+                : p->causal    ? FA_B200_SCHEDULE_PERSISTENT_ROTATED
+                               : FA_B200_SCHEDULE_PERSISTENT_FULL;
+  if (grid != nullptr) *grid = static_cast<int32_t>(pl.grid);
+  return FA_B200_OK;
 }
 
 // ------------------------------------------------------------------------------------ decode
@@ -306,32 +389,18 @@ int64_t fa_b200_decode_workspace_bytes(int32_t B, int32_t H, int32_t kv_len) {
   return static_cast<int64_t>(B) * H * splits * fa::kDecodePartial * static_cast<int64_t>(sizeof(float));
 }
 
-int fa_b200_decode(const fa_b200_decode_params* p) {
-  int rc = decode_validate(p);
-  if (rc != FA_B200_OK) return rc;
-  if (p->B == 0 || p->H == 0) return FA_B200_OK;
-  int splits = 1, rows = 0;
-  bool wide = false;
-  decode_split(p->B, p->H, p->kv_len, &splits, &rows, &wide);
-  if (splits > 1) {
-    const int64_t need = fa_b200_decode_workspace_bytes(p->B, p->H, p->kv_len);
-    if (p->workspace == nullptr || p->workspace_bytes < need ||
-        (reinterpret_cast<uintptr_t>(p->workspace) & 15u))
-      return FA_B200_ERR_WORKSPACE;
-  }
-  DeviceGuard guard(p->device);
-  if (guard.error) return guard.error;
-  DeviceState& st = g_dev[p->device];
-  std::call_once(st.once, init_device, p->device);
-  if (st.init_error) return st.init_error;
+namespace {
 
+// The launch shared by fa_b200_decode and fa_b200_decode_static; they differ only in where the
+// split-KV scratch lives.  `p` has been validated, the device is current and set up.
+int decode_launch(const fa_b200_decode_params* p, float* scratch, int splits, int rows, bool wide) {
   fa::DecodeParams kp;
   kp.q = static_cast<const __nv_bfloat16*>(p->q);
   kp.k = static_cast<const __nv_bfloat16*>(p->k_cache);
   kp.v = static_cast<const __nv_bfloat16*>(p->v_cache);
   kp.o = static_cast<__nv_bfloat16*>(p->o);
   kp.lse = p->lse;
-  kp.scratch = static_cast<float*>(p->workspace);
+  kp.scratch = scratch;
   kp.q_sb = p->q_strides[0]; kp.q_sh = p->q_strides[1];
   kp.o_sb = p->o_strides[0]; kp.o_sh = p->o_strides[1];
   kp.k_sb = p->k_strides[0]; kp.k_sh = p->k_strides[1]; kp.k_sn = p->k_strides[2];
@@ -357,6 +426,28 @@ int fa_b200_decode(const fa_b200_decode_params* p) {
     e = cudaGetLastError();
   }
   return static_cast<int>(e);
+}
+
+}  // namespace
+
+int fa_b200_decode(const fa_b200_decode_params* p) {
+  int rc = decode_validate(p);
+  if (rc != FA_B200_OK) return rc;
+  if (p->B == 0 || p->H == 0) return FA_B200_OK;
+  int splits = 1, rows = 0;
+  bool wide = false;
+  decode_split(p->B, p->H, p->kv_len, &splits, &rows, &wide);
+  if (splits > 1) {
+    const int64_t need = fa_b200_decode_workspace_bytes(p->B, p->H, p->kv_len);
+    if (p->workspace == nullptr || p->workspace_bytes < need ||
+        (reinterpret_cast<uintptr_t>(p->workspace) & 15u))
+      return FA_B200_ERR_WORKSPACE;
+  }
+  DeviceGuard guard(p->device);
+  if (guard.error) return guard.error;
+  DeviceState* stp = nullptr;
+  if ((rc = ready_device(p->device, &stp)) != 0) return rc;
+  return decode_launch(p, static_cast<float*>(p->workspace), splits, rows, wide);
 }
 
 // ----------------------------------------------------------- decode without any allocation
@@ -398,45 +489,12 @@ int fa_b200_decode_static(const fa_b200_decode_params* p) {
 
   DeviceGuard guard(p->device);
   if (guard.error) return guard.error;
-  DeviceState& st = g_dev[p->device];
-  std::call_once(st.once, init_device, p->device);          // architecture check, no allocation
-  if (st.init_error) return st.init_error;
+  DeviceState* stp = nullptr;
+  if ((rc = ready_device(p->device, &stp)) != 0) return rc;   // architecture check, no allocation
   StaticScratchState& ss = g_static_scratch[p->device];
   std::call_once(ss.once, init_static_scratch, p->device);  // first call on this device only
   if (ss.error) return ss.error;
-
-  fa::DecodeParams kp;
-  kp.q = static_cast<const __nv_bfloat16*>(p->q);
-  kp.k = static_cast<const __nv_bfloat16*>(p->k_cache);
-  kp.v = static_cast<const __nv_bfloat16*>(p->v_cache);
-  kp.o = static_cast<__nv_bfloat16*>(p->o);
-  kp.lse = p->lse;
-  kp.scratch = ss.ptr;
-  kp.q_sb = p->q_strides[0]; kp.q_sh = p->q_strides[1];
-  kp.o_sb = p->o_strides[0]; kp.o_sh = p->o_strides[1];
-  kp.k_sb = p->k_strides[0]; kp.k_sh = p->k_strides[1]; kp.k_sn = p->k_strides[2];
-  kp.v_sb = p->v_strides[0]; kp.v_sh = p->v_strides[1]; kp.v_sn = p->v_strides[2];
-  kp.B = p->B; kp.H = p->H; kp.kv_len = p->kv_len;
-  kp.kv_len_ptr = p->kv_len_device;
-  kp.k_new = static_cast<const __nv_bfloat16*>(p->k_new);
-  kp.v_new = static_cast<const __nv_bfloat16*>(p->v_new);
-  kp.new_sb = p->new_strides[0]; kp.new_sh = p->new_strides[1];
-  kp.splits = splits;
-  kp.rows_per_split = rows;
-  const float scale = p->softmax_scale > 0.0f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(p->d));
-  kp.scale_log2 = scale * 1.4426950408889634f;
-
-  const cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
-  const dim3 grid(static_cast<unsigned>(p->B * p->H), static_cast<unsigned>(splits));
-  if (wide) fa::fa_decode_partial_kernel<fa::kDecodeWideThreads><<<grid, fa::kDecodeWideThreads, 0, stream>>>(kp);
-  else fa::fa_decode_partial_kernel<fa::kDecodeThreads><<<grid, fa::kDecodeThreads, 0, stream>>>(kp);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return static_cast<int>(e);
-  if (splits > 1) {
-    fa::fa_decode_combine_kernel<<<static_cast<unsigned>(p->B * p->H), 64, 0, stream>>>(kp);
-    e = cudaGetLastError();
-  }
-  return static_cast<int>(e);
+  return decode_launch(p, ss.ptr, splits, rows, wide);
 }
 
 int fa_b200_device_ok(int device) {

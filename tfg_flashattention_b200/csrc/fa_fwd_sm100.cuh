@@ -136,21 +136,23 @@ struct FwdParams {
   unsigned int* status;       // [4] watchdog words in global memory
 };
 
-// Optional timeline trace (compile with -DFA_TRACE): the CTA named by g_fa_trace_block stores
-// clock64() stamps of its role hand-offs; read back with fa_b200_trace_read().  Not compiled
-// into the product library.
+// Optional timeline trace (compile with -DFA_TRACE; timeline.py builds that variant into a library
+// of its own): lane 0 of softmax warps 0 and 3 and of the issuer warp of the CTA named by
+// g_fa_trace_block store clock64() stamps of their hand-offs for the first 64 tiles.  The product
+// library is built without it and carries none of this.
 #ifdef FA_TRACE
-constexpr int kTraceSlots = 8192;
+constexpr int kTraceRoles = 4, kTraceTiles = 64, kTraceEvents = 16;
+constexpr int kTraceSlots = kTraceRoles * kTraceTiles * kTraceEvents;
 __device__ unsigned long long g_fa_trace[kTraceSlots];
 __device__ int g_fa_trace_block = 0;
-// layout: role r (0 = softmax row 0; 2 = issuer), iteration j (< 64), event e (< 16)
-#define FA_TRACE_EVENT(role, j, e)                                                   \
-  do {                                                                               \
-    if (blockIdx.x == g_fa_trace_block && (j) < 64)                                  \
-      g_fa_trace[((role) * 64 + (j)) * 16 + (e)] = clock64();                        \
+#define FA_TRACE_EVENT(role, g, e)                                                     \
+  do {                                                                                 \
+    if ((role) >= 0 && (threadIdx.x & 31) == 0 && blockIdx.x == g_fa_trace_block &&    \
+        (g) < kTraceTiles)                                                             \
+      g_fa_trace[((role) * kTraceTiles + (g)) * kTraceEvents + (e)] = clock64();       \
   } while (0)
 #else
-#define FA_TRACE_EVENT(role, j, e) do {} while (0)
+#define FA_TRACE_EVENT(role, g, e) do {} while (0)
 #endif
 
 struct Watch {
@@ -394,24 +396,31 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           const int itk = it + 1;      // the next K in ring order: K_{j+1}, or K_0 of the next item
           const bool last = j + 1 == w.ns;
           // ---- S for the next tile, as soon as the softmax warps hold S(g) in registers
+          FA_TRACE_EVENT(2, g, 0);
           if (!last || has_next_item) {
             if (last)   // the next item's Q must have landed (its load waited for q_empty)
               ok = wait_bar_warp(smem_u32(&sm.q_full), (n + 1) & 1, watch, kWaitQFull);
             ok = ok &&
-                 wait_bar_warp(smem_u32(&sm.kv_full[slot_of(itk)]), par_of(itk), watch, kWaitKVFull) &&
-                 wait_bar_warp(smem_u32(&sm.s_free), g & 1, watch, kWaitSFree);
+                 wait_bar_warp(smem_u32(&sm.kv_full[slot_of(itk)]), par_of(itk), watch, kWaitKVFull);
+            FA_TRACE_EVENT(2, g, 1);
+            ok = ok && wait_bar_warp(smem_u32(&sm.s_free), g & 1, watch, kWaitSFree);
             if (!ok) break;
+            FA_TRACE_EVENT(2, g, 2);
             tc_fence_after();
             issue_s(slot_of(itk), last ? wn.ns == 1 : j + 2 == w.ns);
+            FA_TRACE_EVENT(2, g, 3);
           }
           // ---- O += P V for this tile
-          ok = wait_bar_warp(smem_u32(&sm.kv_full[slot_of(itv)]), par_of(itv), watch, kWaitKVFull) &&
-               wait_bar_warp(smem_u32(&sm.p_full), g & 1, watch, kWaitPFull);
+          ok = wait_bar_warp(smem_u32(&sm.kv_full[slot_of(itv)]), par_of(itv), watch, kWaitKVFull);
+          FA_TRACE_EVENT(2, g, 4);
+          ok = ok && wait_bar_warp(smem_u32(&sm.p_full), g & 1, watch, kWaitPFull);
           if (ok && j == 0 && n > 0)   // the previous item's epilogue must have read O
             ok = wait_bar_warp(smem_u32(&sm.o_free), (n - 1) & 1, watch, kWaitOFree);
           if (!ok) break;
+          FA_TRACE_EVENT(2, g, 5);
           tc_fence_after();
           issue_pv(slot_of(itv), j == 0);
+          FA_TRACE_EVENT(2, g, 6);
           it += 2;
         }
         w = wn;
@@ -436,6 +445,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     bool ok = true;
     int g = 0;   // running tile counter across work items (selects the barrier phases)
     int n = 0;   // local work-item counter
+#ifdef FA_TRACE
+    const int trole = warp == 0 ? 0 : (warp == 3 ? 1 : -1);
+#endif
 
     // A finished item whose epilogue is still owed.  It is run in the middle of the NEXT item's
     // first tile (after that tile's P is stored, before the issuer is told about it): by then the
@@ -507,8 +519,11 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       float l = 0.f;                // running sum of exp2((s - m_ref) * c)
 
       for (int j = 0; j < w.ns; ++j, ++g) {
+        FA_TRACE_EVENT(trole, g, 0);
+        if (j == 0) FA_TRACE_EVENT(trole, g, 9);
         ok = wait_bar_warp(bar_s_full, g & 1, watch, kWaitSFull);
         if (!ok) break;
+        FA_TRACE_EVENT(trole, g, 1);
         tc_fence_after();
         uint32_t sv[kBlockN];
         {  // two 64-column loads: a single 128-register instruction does not fit the 128-register
@@ -519,6 +534,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           tmem_ld_nowait_x64(t_s + 64, hi);
           tmem_wait_ld_fence(sv);
         }
+        FA_TRACE_EVENT(trole, g, 2);
         // S is in registers: let the issuer overwrite it with the next tile's scores
         tc_fence_before();
         __syncwarp();
@@ -566,10 +582,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
 
         // O += P V of the previous tile (of this or the previous item) must be finished before P
         // is overwritten or O is touched
+        FA_TRACE_EVENT(trole, g, 3);
         if (g > 0) {
           ok = wait_bar_warp(bar_o, (g - 1) & 1, watch, kWaitOFull);
           if (!ok) break;
         }
+        FA_TRACE_EVENT(trole, g, 4);
         if (j == 0) {
           m_ref = m_new;
         } else {
@@ -630,7 +648,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           unpack_f32x2(lsum1, l2, l3);
           l += (l0 + l1) + (l2 + l3);
         }
+        FA_TRACE_EVENT(trole, g, 5);
         tmem_wait_st();
+        FA_TRACE_EVENT(trole, g, 6);
 
         // the epilogue owed to the previous item: its O is final (the wait above covered its last
         // PV) and must be read before the issuer accumulates this item's first P V into O
@@ -639,9 +659,11 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           if (!ok) break;
         }
 
+        FA_TRACE_EVENT(trole, g, 7);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_p);
+        FA_TRACE_EVENT(trole, g, 8);
       }
       if (!ok) break;
       sm.owed[r] = make_float2(1.0f / l, m_ref * c + log2f(l));   // read back by this same thread

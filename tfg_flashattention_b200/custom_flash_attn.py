@@ -29,7 +29,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["forward", "forward_host", "decode", "last_status"]
+__all__ = ["forward", "forward_host", "decode", "last_status", "plan"]
 
 
 def _check_input(t: torch.Tensor, name: str) -> None:
@@ -59,26 +59,9 @@ def _strides3(t: torch.Tensor, name: str):
     return (ctypes.c_int64 * 3)(sb, sh, sn)
 
 
-def forward(Q, K, V, causal=True, return_lse=False, softmax_scale=None, out=None):
-    """Attention forward on the current CUDA stream of Q's device.  See the module docstring."""
-    _check_input(Q, "Q")
-    _check_input(K, "K_mat")
-    _check_input(V, "V")
-    if K.shape != Q.shape or V.shape != Q.shape:
-        raise RuntimeError("Q, K_mat and V must have the same shape [B, H, N, d]")
-    if K.device != Q.device or V.device != Q.device:
-        raise RuntimeError("Q, K_mat and V must be on the same device")
+def _fwd_params(Q, K, V, O, lse, causal, softmax_scale):
+    """struct fa_b200_params for one call on the current stream of Q's device."""
     B, H, N, d = Q.shape
-    if out is None:
-        O = torch.empty_like(Q)      # same allocation rule as the reference (torch_bind.cpp:31)
-    else:
-        _check_input(out, "out")
-        if out.shape != Q.shape or out.device != Q.device:
-            raise RuntimeError("out must match Q in shape and device")
-        O = out
-    lse = torch.empty((B, H, N), dtype=torch.float32, device=Q.device) if return_lse else None
-
-    lib = _lib.load()
     p = _lib.FaParams()
     p.q, p.k, p.v, p.o = Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr()
     p.lse = lse.data_ptr() if lse is not None else None
@@ -97,10 +80,49 @@ def forward(Q, K, V, causal=True, return_lse=False, softmax_scale=None, out=None
     p.causal = 1 if causal else 0
     p.device = Q.device.index if Q.device.index is not None else torch.cuda.current_device()
     p.stream = torch.cuda.current_stream(Q.device).cuda_stream
-    rc = lib.fa_b200_fwd(ctypes.byref(p))
+    return p
+
+
+def _check_qkv(Q, K, V):
+    _check_input(Q, "Q")
+    _check_input(K, "K_mat")
+    _check_input(V, "V")
+    if K.shape != Q.shape or V.shape != Q.shape:
+        raise RuntimeError("Q, K_mat and V must have the same shape [B, H, N, d]")
+    if K.device != Q.device or V.device != Q.device:
+        raise RuntimeError("Q, K_mat and V must be on the same device")
+
+
+def forward(Q, K, V, causal=True, return_lse=False, softmax_scale=None, out=None):
+    """Attention forward on the current CUDA stream of Q's device.  See the module docstring."""
+    _check_qkv(Q, K, V)
+    B, H, N, d = Q.shape
+    if out is None:
+        O = torch.empty_like(Q)      # same allocation rule as the reference (torch_bind.cpp:31)
+    else:
+        _check_input(out, "out")
+        if out.shape != Q.shape or out.device != Q.device:
+            raise RuntimeError("out must match Q in shape and device")
+        O = out
+    lse = torch.empty((B, H, N), dtype=torch.float32, device=Q.device) if return_lse else None
+    p = _fwd_params(Q, K, V, O, lse, causal, softmax_scale)
+    rc = _lib.load().fa_b200_fwd(ctypes.byref(p))
     if rc != 0:
         raise RuntimeError(f"custom_flash_attn.forward failed ({rc}): {_lib.strerror(rc)}")
     return (O, lse) if return_lse else O
+
+
+def plan(Q, K, V, causal=True):
+    """Which kernel schedule `forward` would use for these tensors, without launching anything:
+    (name, grid) with name one of "cta_per_tile", "persistent_paired", "persistent_rotated",
+    "persistent_full", "none" (fa_b200_fwd_plan in include/fa_b200.h)."""
+    _check_qkv(Q, K, V)
+    p = _fwd_params(Q, K, V, Q, None, causal, None)
+    schedule, grid = ctypes.c_int32(-1), ctypes.c_int32(0)
+    rc = _lib.load().fa_b200_fwd_plan(ctypes.byref(p), ctypes.byref(schedule), ctypes.byref(grid))
+    if rc != 0:
+        raise RuntimeError(f"custom_flash_attn.plan failed ({rc}): {_lib.strerror(rc)}")
+    return _lib.SCHEDULES[schedule.value], grid.value
 
 
 _decode_workspaces = {}

@@ -1,7 +1,8 @@
 """GPT-2 prefill harness: the caller of the attention hot path.
 
 Mirrors the reference's model (src/py/model_inference.py:39-190) module for module and parameter
-name for parameter name, so a reference state_dict loads unchanged:
+name for parameter name, so a reference state_dict loads unchanged (strict=True, including the
+`att.mask` buffers the reference stores, which are dropped on load and regenerated on export):
 
     MultiHeadAttention  :39-94    W_query / W_key / W_value / out_proj, impl_type dispatch
     LayerNorm           :96-107   scale / shift, eps 1e-5, biased variance
@@ -106,6 +107,23 @@ class MultiHeadAttention(nn.Module):
         self._qkv_w = None      # fused [3*d_out, d_in] weight / [3*d_out] bias (inference cache)
         self._qkv_b = None
         self.small_linear = False   # set by GPTModel.prepare_for_inference on the bf16 GPU path
+        # The reference registers the causal mask as a persistent buffer (model_inference.py:55),
+        # so its state_dicts carry a `mask` entry per attention module.  Nothing here reads a mask
+        # (the kernel masks by index), so none is stored -- context_length^2 floats per layer --
+        # but state_dicts stay interchangeable in both directions: the entry is accepted and
+        # dropped on load, and written (built on the fly) on export.
+        self._register_load_state_dict_pre_hook(self._drop_mask_on_load)
+        self._register_state_dict_hook(self._add_mask_on_export)
+
+    @staticmethod
+    def _drop_mask_on_load(state_dict, prefix, *_):
+        state_dict.pop(prefix + "mask", None)
+
+    @staticmethod
+    def _add_mask_on_export(module, state_dict, prefix, _local_metadata):
+        ref = module.W_query.weight
+        n = module.context_length
+        state_dict[prefix + "mask"] = torch.triu(torch.ones(n, n, device=ref.device), diagonal=1)
 
     def fuse_qkv(self):
         """Cache the concatenated projection (call again after changing the weights)."""
