@@ -18,8 +18,17 @@ measured bf16 tensor peak; `cpu_baseline` times the CPU oracle (a port of the re
 standard-PyTorch attention) on a bounded sample on this box's host cores; `extra.sweep` holds the
 other attention configurations (sharded over ranks by (batch, head)).
 
-`--impl reference` times that CPU implementation instead, on all host threads, one bounded sample
-per step, and prints the same line with "impl": "reference".
+`--impl reference` runs the reference project's own implementation of the path instead -- its
+CUDA kernel, compiled unmodified from the reference sources by oracle/build_ref.py and checked
+against the CPU oracle on a small shape before it is timed -- on the same workload, metric and
+unit, one replica per rank, and prints the same line with "impl": "reference"; its `cpu_baseline`
+is the CPU port of the reference's standard-PyTorch attention on a bounded sample.  Where that
+library is absent (it is built only where the reference sources are), the CPU port is what is timed.
+
+The timed region of the headline is K steps repeated back to back until it spans at least 200 ms
+(`timed_launches` of them; `ms_per_step` is the mean over all), so that the maximum over ranks is not
+decided by a few microseconds of launch jitter; `roofline.sustained` is the same launch kept going
+for two seconds with the clocks sampled through it.
 """
 from __future__ import annotations
 
@@ -45,7 +54,10 @@ UNIT = "TFLOP/s"
 # dram__bytes_write.sum).  Captured with ncu at B=12 (118.03 + 18.10 MB per launch) and scaled by
 # 32/12 to the benchmark's B=32: every (batch, head) is independent, so traffic grows in proportion.
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 136.13e6 * 32 / 12
+NCU_TRAFFIC_NOTE = ("ncu capture at B=12 scaled by 32/12; reads equal Q+K+V exactly, writes are a lower bound "
+                    "(part of O is still in L2 when the small capture's kernel ends)")
 E2E_CHUNKS = 8                # batch slices the host-buffer call pipelines through PCIe
+E2E_CHUNKS_MULTI = 4          # fewer, larger copies when several ranks share the host's memory system
 CPU_SAMPLE_BATCH = 4          # batch entries (x25 heads) the CPU legs compute per repetition
 
 
@@ -167,29 +179,96 @@ def n_input_sets(q):
     return max(1, min(8, -(-400_000_000 // one_set)))
 
 
-def time_kernel(cfa, q, k, v, causal, steps, warmup, world):
+def gather_over_ranks(x: float, world: int):
+    if world == 1:
+        return [x]
+    import torch.distributed as dist
+    t = torch.tensor([x], device="cuda", dtype=torch.float64)
+    out = [torch.zeros_like(t) for _ in range(world)]
+    dist.all_gather(out, t)
+    return [float(o.item()) for o in out]
+
+
+def time_kernel(cfa, q, k, v, causal, steps, warmup, world, min_window_ms=0.0, detail=None):
     """ms per step, max over ranks; CUDA events on the launching (current torch) stream.  Small
-    problems rotate through several copies of their inputs (n_input_sets)."""
+    problems rotate through several copies of their inputs (n_input_sets).  With min_window_ms the
+    block of `steps` launches is repeated back to back (same event pair) until the timed region is
+    at least that long; `detail`, a dict, receives the launch count and the per-rank figures."""
     sets = [(q, k, v, torch.empty_like(q))]
     for _ in range(n_input_sets(q) - 1):
         sets.append((q.clone(), k.clone(), v.clone(), torch.empty_like(q)))
     n = len(sets)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
     for i in range(max(warmup, n)):
         qq, kk, vv, oo = sets[i % n]
         cfa.forward(qq, kk, vv, causal=causal, out=oo)
+    e1.record()
+    torch.cuda.synchronize()
+    repeats = 1
+    if min_window_ms > 0:
+        est = max_over_ranks(e0.elapsed_time(e1) / max(warmup, n), world)     # same count on every rank
+        repeats = max(1, int(-(-min_window_ms // max(est * steps, 1e-6))))
+    launches = steps * repeats
     barrier(world)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(steps):
+    for i in range(launches):
         qq, kk, vv, oo = sets[i % n]
         cfa.forward(qq, kk, vv, causal=causal, out=oo)
     e1.record()
     barrier(world)
-    ms = e0.elapsed_time(e1) / steps
+    ms = e0.elapsed_time(e1) / launches
+    if detail is not None:
+        detail["timed_launches"] = launches
+        detail["ms_per_step_by_rank"] = [round(x, 5) for x in gather_over_ranks(ms, world)]
     return max_over_ranks(ms, world)
 
 
-def time_e2e(cfa, w, rank, steps, warmup, world):
+def time_sustained(cfa, q, k, v, seconds, sampler_id):
+    """The headline launch back to back for `seconds`, clocks sampled through it (this rank only):
+    what the kernel holds once power and temperature have settled, next to the burst figure."""
+    sets = [(q, k, v, torch.empty_like(q))]
+    sampler = ClockSampler(sampler_id)
+    sampler.start()
+    time.sleep(0.3)
+    torch.cuda.synchronize()
+    t0 = time.time()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches = 0
+    e0.record()
+    while time.time() - t0 < seconds:
+        for _ in range(200):
+            cfa.forward(q, k, v, causal=True, out=sets[0][3])
+        launches += 200
+    e1.record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    clocks = sampler.stop(t0, t1)
+    return e0.elapsed_time(e1) / launches, launches, clocks
+
+
+def bind_near_gpu(local):
+    """Run this rank (and so allocate its pinned host buffers, first touch) on the cores nearest
+    its GPU, as `nvidia-smi topo -m` reports them.  Returns the CPU set used, or None."""
+    try:
+        out = subprocess.run(["nvidia-smi", "topo", "-m"], capture_output=True, text=True, timeout=20).stdout
+        for line in out.splitlines():
+            f = line.split()
+            if f and f[0] == f"GPU{local}":
+                for tok in f[1:]:
+                    if tok[0].isdigit() and ("-" in tok or "," in tok):
+                        cpus = set()
+                        for part in tok.split(","):
+                            lo, _, hi = part.partition("-")
+                            cpus.update(range(int(lo), int(hi or lo) + 1))
+                        os.sched_setaffinity(0, cpus)
+                        return tok
+    except Exception:
+        pass
+    return None
+
+
+def time_e2e(cfa, w, rank, steps, warmup, world, detail=None):
     """ms per step through the public host-buffer call (custom_flash_attn.forward_host): pinned
     q, k, v -> device, forward, O -> pinned host, all inside the timed region; the call cuts the
     batch into slices so that uploads, kernels and downloads overlap."""
@@ -200,7 +279,7 @@ def time_e2e(cfa, w, rank, steps, warmup, world):
 
     def step():
         # the public host-buffer call: chunked upload / kernel / download pipeline
-        cfa.forward_host(hq, hk, hv, out=ho, chunks=E2E_CHUNKS)
+        cfa.forward_host(hq, hk, hv, out=ho, chunks=E2E_CHUNKS if world == 1 else E2E_CHUNKS_MULTI)
 
     for _ in range(max(1, warmup)):
         step()
@@ -211,8 +290,13 @@ def time_e2e(cfa, w, rank, steps, warmup, world):
         step()
     e1.record()
     barrier(world)
-    ms = max_over_ranks(e0.elapsed_time(e1) / steps, world)
+    mine = e0.elapsed_time(e1) / steps
+    ms = max_over_ranks(mine, world)
     nbytes = hq.numel() * 2
+    if detail is not None:
+        detail["ms_per_step_by_rank"] = [round(x, 3) for x in gather_over_ranks(mine, world)]
+        detail["host_link_gbs_by_rank"] = [round(4 * nbytes / (x * 1e-3) / 1e9, 1)
+                                           for x in gather_over_ranks(mine, world)]
     return ms, 3 * nbytes, nbytes
 
 
@@ -304,39 +388,178 @@ def bench_config(w):
             "sharding": "independent (batch, head) problems per GPU, no collective"}
 
 
+def time_rotating(fn, q, k, v, steps, warmup):
+    """ms per call of fn(q, k, v, out) on this rank, rotating input copies like time_kernel."""
+    sets = [(q, k, v, torch.empty_like(q))]
+    for _ in range(n_input_sets(q) - 1):
+        sets.append((q.clone(), k.clone(), v.clone(), torch.empty_like(q)))
+    n = len(sets)
+    for i in range(max(warmup, n)):
+        fn(*sets[i % n])
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(*sets[i % n])
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def reference_kernel_checked():
+    """The reference project's CUDA kernel (oracle/_ref), or None with a reason.  Before anything
+    is timed it is run once on a small ragged shape and compared with the CPU oracle."""
+    from oracle import ref_kernel
+    if not ref_kernel.available():
+        return None, "oracle/_ref/libref_v1.so absent (built by oracle/build_ref.py where the reference sources are)"
+    if not torch.cuda.is_available():
+        return None, "no CUDA device"
+    from oracle.attention_oracle import manual_attention
+    g = torch.Generator().manual_seed(5)
+    q, k, v = (torch.randn(2, 3, 200, 64, generator=g).bfloat16() for _ in range(3))
+    o = ref_kernel.forward(q.cuda(), k.cuda(), v.cuda()).float().cpu()
+    ref = manual_attention(q.float(), k.float(), v.float(), causal=True)
+    err = (o - ref).abs().max().item()
+    if not err <= 2e-2:
+        return None, f"reference kernel disagrees with the oracle on the check shape (max-abs {err:.3e})"
+    return ref_kernel, None
+
+
+def run_comparators(cfa, peaks):
+    """Other implementations of the same problem, timed on this rank in the same run (timing only):
+    torch's scaled_dot_product_attention -- what every reference test compares with
+    (test/py/test_cuda_implementation.py:49-52, 83, 112) -- with its default, flash and cuDNN
+    back ends, and the reference project's own CUDA kernel (always causal)."""
+    import torch.nn.functional as F
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+    ref_kernel, why = reference_kernel_checked()
+    rows = []
+    shapes = [("headline B=32 H=25 N=1024", workloads.config4_attention()), ("config 1", workloads.config1()),
+              ("config 3 N=4096", workloads.config3(4096, True)), ("config 3 N=4096", workloads.config3(4096, False))]
+    for label, w in shapes:
+        q, k, v = device_inputs(w, 0)
+        steps = 20 if w.N <= 1024 else 8
+        row = {"workload": label, "B": w.B, "H": w.H, "N": w.N, "causal": w.causal}
+        def tf(ms):
+            return round(w.flops() / (ms * 1e-3) / 1e12, 1)
+        ms = time_rotating(lambda a, b, c, o: cfa.forward(a, b, c, causal=w.causal, out=o), q, k, v, steps, 3)
+        row["this_library"] = {"ms": round(ms, 4), "tflops": tf(ms)}
+        for name, backend in (("sdpa_default", None), ("sdpa_flash", SDPBackend.FLASH_ATTENTION),
+                              ("sdpa_cudnn", SDPBackend.CUDNN_ATTENTION)):
+            try:
+                fn = lambda a, b, c, o: F.scaled_dot_product_attention(a, b, c, is_causal=w.causal)
+                if backend is None:
+                    ms = time_rotating(fn, q, k, v, steps, 3)
+                else:
+                    with sdpa_kernel(backend):
+                        ms = time_rotating(fn, q, k, v, steps, 3)
+                row[name] = {"ms": round(ms, 4), "tflops": tf(ms)}
+            except Exception as e:   # a back end that refuses the shape
+                row[name] = {"unavailable": str(e).splitlines()[0][:120]}
+        if not w.causal:
+            row["reference_v1_kernel"] = {"unavailable": "the reference kernel is always causal"}
+        elif ref_kernel is None:
+            row["reference_v1_kernel"] = {"unavailable": why}
+        else:
+            ms = time_rotating(lambda a, b, c, o: ref_kernel.forward(a, b, c, out=o), q, k, v, 3, 1)
+            row["reference_v1_kernel"] = {"ms": round(ms, 3), "tflops": tf(ms)}
+        for name in ("sdpa_default", "sdpa_flash", "sdpa_cudnn", "reference_v1_kernel"):
+            if "ms" in row[name]:
+                row[name]["this_library_speedup"] = round(row[name]["ms"] / row["this_library"]["ms"], 2)
+        rows.append(row)
+        del q, k, v
+        torch.cuda.empty_cache()
+    return rows
+
+
 def run_reference(args, w):
-    """The reference arm: the reference's standard-PyTorch attention (CPU port in oracle/) on all
-    host threads; one bounded sample per step."""
+    """The reference arm.  The reference's implementation of this path is its CUDA kernel
+    (src/cpp/v1.cu + headers/v1_implementation.hpp): it is what is timed, one replica per rank on
+    the same workload, `value` with inputs resident in HBM and `e2e` through host buffers (pinned
+    host -> device copies of q, k, v, kernel, device -> host copy of O inside the timed region,
+    which is what a caller of the reference binding with host data has to do).  `cpu_baseline` is
+    the CPU port of the reference's standard-PyTorch attention on a bounded sample (rank 0).
+    Where the reference kernel is not available the CPU port is what is timed, on rank 0 alone."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
+    ref_kernel, why = reference_kernel_checked() if torch.cuda.is_available() else (None, "no CUDA device")
     threads = os.cpu_count() or 1
-    from oracle.attention_oracle import manual_attention
-    torch.set_num_threads(threads)
-    bs = min(CPU_SAMPLE_BATCH, w.B)
-    g = torch.Generator().manual_seed(w.seed)
-    q, k, v = (torch.randn(bs, w.H, w.N, w.d, generator=g) for _ in range(3))
-    flops = 2.0 * bs * w.H * w.N * w.N * w.d
-    for _ in range(args.warmup):
-        manual_attention(q, k, v, causal=True)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        manual_attention(q, k, v, causal=True)
-    dt = (time.perf_counter() - t0) / args.steps
-    val = flops / dt / 1e12
-    sample = f"{bs} of {w.B} batch entries ({bs * w.H} of {w.B * w.H} heads) per step, fp32, torch CPU"
-    line = {
-        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic",
-        "config": dict(bench_config(w), note="CPU implementation; runs on rank 0 only, value does not scale with --gpus"),
-        "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
-        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
-    }
-    print(json.dumps(line), flush=True)
+    if ref_kernel is None:
+        if rank != 0:
+            return
+        tf, bs, times = cpu_attention_sample(w, reps=max(1, args.steps), threads=threads)
+        sample = f"{bs} of {w.B} batch entries ({bs * w.H} of {w.B * w.H} heads) per step, fp32, torch CPU"
+        dt = statistics.median(times)
+        line = {
+            "impl": "reference", "metric": METRIC, "value": tf, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": bench_config(w),
+            "note": f"reference CUDA kernel unavailable ({why}): CPU port timed on rank 0 only, value does not scale with --gpus",
+            "cpu_baseline": {"value": tf, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": tf, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+        }
+        print(json.dumps(line), flush=True)
+        return
+
+    world, rank, local = dist_setup(args.gpus)
+    torch.cuda.set_device(local)
+    # the reference launcher launches on the current device's legacy default stream (v1.cu:33-34;
+    # its query of device 0's properties, :7-8, only feeds dead code): one replica per rank
+    q, k, v = device_inputs(w, rank)
+    o = torch.empty_like(q)
+    steps, warmup = max(1, args.steps), max(1, args.warmup)
+    for _ in range(warmup):
+        ref_kernel.forward(q, k, v, out=o)
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        ref_kernel.forward(q, k, v, out=o)
+    e1.record()
+    barrier(world)
+    ms = max_over_ranks(e0.elapsed_time(e1) / steps, world)
+    value = world * w.flops() / (ms * 1e-3) / 1e12
+    # end to end with host buffers
+    hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+    ho = torch.empty_like(hq).pin_memory()
+    def e2e_step():
+        dq, dk, dv = (t.to("cuda", non_blocking=True) for t in (hq, hk, hv))
+        ho.copy_(ref_kernel.forward(dq, dk, dv), non_blocking=True)
+    e2e_step()
+    barrier(world)
+    n_e2e = max(2, min(steps, 5))
+    e0.record()
+    for _ in range(n_e2e):
+        e2e_step()
+    e1.record()
+    barrier(world)
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1) / n_e2e, world)
+    nbytes = hq.numel() * 2
+    cpu = None
+    if rank == 0:
+        tf, bs, times = cpu_attention_sample(w, reps=3, threads=threads)
+        cpu = {"value": tf, "unit": UNIT, "cores": threads, "kind": "port",
+               "sample": f"{bs} of {w.B} batch entries ({bs * w.H} of {w.B * w.H} heads), median of "
+                         f"{len(times)} repetitions, fp32 torch CPU (the reference's standard-PyTorch branch)"}
+        line = {
+            "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+            "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": bench_config(w),
+            "note": "the reference project's own CUDA kernel (flash_attention_forward_kernel<32,32,2,64,bf16>, "
+                    "fp32 FMA, no tensor cores), compiled unmodified for sm_100a, one replica per rank",
+            "reference_kind": "reference CUDA kernel (oracle/_ref/libref_v1.so)",
+            "cpu_baseline": cpu,
+            "e2e": {"value": world * w.flops() / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": 3 * nbytes, "d2h_bytes_per_step": nbytes},
+            "gpu_launches": steps,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
 
 
 def main():
@@ -423,7 +646,8 @@ def main():
     sampler.start()
     time.sleep(0.3)
     t0 = time.time()
-    ms = time_kernel(cfa, q, k, v, True, args.steps, args.warmup, world)
+    headline = {}
+    ms = time_kernel(cfa, q, k, v, True, args.steps, args.warmup, world, min_window_ms=200.0, detail=headline)
     t1 = time.time()
     clocks = sampler.stop(t0, t1)
     status = cfa.last_status()
@@ -432,10 +656,23 @@ def main():
     flops = w.flops()
     value = world * flops / (ms * 1e-3) / 1e12
     per_gpu = value / world
+    # the same launch kept going for two seconds: what it holds at settled clocks and power
+    sus_ms, sus_launches, sus_clocks = time_sustained(cfa, q, k, v, 2.0, gpu_id)
+    sus_tf = flops / (sus_ms * 1e-3) / 1e12
+    sustained = {"tflops": round(sus_tf, 1), "ms_per_launch": round(sus_ms, 5), "launches": sus_launches,
+                 "seconds": round(sus_ms * sus_launches * 1e-3, 2),
+                 "sm_mhz_median": sus_clocks.get("sm_mhz"), "power_w_max": sus_clocks.get("power_w_max"),
+                 "reasons": sus_clocks.get("reasons"),
+                 "frac_of_sustained_peak": round(sus_tf / peaks["bf16_tflops_sustained"], 4) if peaks["bf16_tflops_sustained"] else None,
+                 "frac_of_burst_peak": round(sus_tf / peaks["bf16_tflops"], 4),
+                 "ms_times_sm_mhz": round(sus_ms * (sus_clocks.get("sm_mhz") or 0), 2),
+                 "burst_ms_times_sm_mhz": round(ms * (clocks.get("sm_mhz") or 0), 2)}
     del q, k, v
 
     # ---------------------------------------------------------------- end to end with host buffers
-    e2e_ms, h2d, d2h = time_e2e(cfa, w, rank, max(3, min(args.steps, 10)), 2, world)
+    cpu_set = bind_near_gpu(local) if world > 1 else None
+    e2e_detail = {"cpu_affinity": cpu_set, "chunks": E2E_CHUNKS if world == 1 else E2E_CHUNKS_MULTI}
+    e2e_ms, h2d, d2h = time_e2e(cfa, w, rank, max(3, min(args.steps, 10)), 2, world, detail=e2e_detail)
     e2e_value = world * flops / (e2e_ms * 1e-3) / 1e12
 
     # ---------------------------------------------------------------- the other attention configs
@@ -599,6 +836,50 @@ def main():
     if world > 1:
         barrier(world)
 
+    # ---------------------------------------------------------------- a small problem: host cost vs kernel
+    small = None
+    comparators = None
+    if not args.no_sweep and rank == 0 and world == 1:
+        cw = workloads.config1()
+        cq, ck, cv = device_inputs(cw, rank)
+        co = torch.empty_like(cq)
+        for _ in range(5):
+            cfa.forward(cq, ck, cv, out=co)
+        torch.cuda.synchronize()
+        # host time of one call: launches into an idle stream, nothing to wait for
+        t_host = []
+        for _ in range(200):
+            torch.cuda.synchronize()
+            h0 = time.perf_counter()
+            cfa.forward(cq, ck, cv, out=co)
+            t_host.append(time.perf_counter() - h0)
+        # kernel alone: the launches recorded once as a CUDA graph and replayed
+        n_rec = 50
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(n_rec):
+                cfa.forward(cq, ck, cv, out=co)
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        g_us = e0.elapsed_time(e1) / n_rec * 1e3
+        e_ms = time_rotating(lambda a, b, c, o: cfa.forward(a, b, c, out=o), cq, ck, cv, 200, 5)
+        small = {"workload": "config 1 (B=4 H=12 N=1024 causal)",
+                 "host_us_per_call_median": round(statistics.median(t_host) * 1e6, 2),
+                 "eager_us_per_launch": round(e_ms * 1e3, 2),
+                 "eager_tflops": round(cw.flops() / (e_ms * 1e-3) / 1e12, 1),
+                 "graph_replay_us_per_launch": round(g_us, 2),
+                 "graph_replay_tflops": round(cw.flops() / (g_us * 1e-6) / 1e12, 1),
+                 "note": "graph replay: same buffers every launch (25 MB, L2-resident); eager: rotating copies"}
+        del graph, cq, ck, cv, co
+        comparators = run_comparators(cfa, peaks)
+        if cfa.last_status() != 0:
+            raise SystemExit("kernel watchdog fired during the comparator runs")
+
     # ---------------------------------------------------------------- CPU baseline (rank 0, N=1 only)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -620,14 +901,18 @@ def main():
             "frac_of_bf16_nominal_2250": per_gpu / 2250.0,
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["bf16_tflops"],
                          "unit": "TFLOP/s", "frac": per_gpu / peaks["bf16_tflops"],
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": f"of {peaks['source']}",
-                         "algorithmic_bytes": w.bytes(), "kernel": "fa::fa_fwd_kernel<true, true> (persistent, causal instantiation)"},
-            "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": args.steps,
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "traffic_note": NCU_TRAFFIC_NOTE,
+                         "peak_source": f"of {peaks['source']}",
+                         "algorithmic_bytes": w.bytes(), "kernel": "fa::fa_fwd_kernel<true, true> (persistent, causal instantiation)",
+                         "sustained": sustained},
+            "e2e": dict({"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms,
+                         "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}, **e2e_detail),
+            "timed_launches": headline.get("timed_launches"),
+            "gpu_launches": headline.get("timed_launches"),
             "clocks": clocks,
             "cpu_baseline": cpu,
-            "extra": {"sweep": sweep, "gpt2_prefill": prefill, "decode_step": decode, "add_layernorm": add_ln, "linear_small": lin,
+            "extra": {"ms_per_step_by_rank": headline.get("ms_per_step_by_rank"), "comparators": comparators,
+                      "small_problem": small, "sweep": sweep, "gpt2_prefill": prefill, "decode_step": decode, "add_layernorm": add_ln, "linear_small": lin,
                       "generate_20_tokens": gen},
         }
         print(json.dumps(line), flush=True)

@@ -729,6 +729,9 @@ const char* fa_b200_strerror(int code) {
       case fa::kWaitKVEmpty: return "fa_b200 watchdog: wait for a free K/V slot ran out";
       case fa::kWaitSFull: return "fa_b200 watchdog: wait for S = QK^T ran out";
       case fa::kWaitPFull: return "fa_b200 watchdog: wait for P from the softmax warps ran out";
+      case fa::kWaitSFree: return "fa_b200 watchdog: wait for the softmax warps to take S ran out";
+      case fa::kWaitOFree: return "fa_b200 watchdog: wait for the epilogue to read O ran out";
+      case fa::kWaitQEmpty: return "fa_b200 watchdog: wait for the Q slot to be released ran out";
       case fa::kWaitOFull: return "fa_b200 watchdog: wait for O += PV ran out";
       default: return "fa_b200 watchdog: a bounded wait ran out";
     }

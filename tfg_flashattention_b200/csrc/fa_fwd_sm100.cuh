@@ -52,6 +52,7 @@ constexpr int kMmaWarp = 4;
 constexpr int kLoadWarp = 5;
 constexpr int kNumThreads = 256;       // two whole warpgroups
 constexpr int kCtasPerSm = 2;
+constexpr int kSmCountHint = 148;      // B200; only decorrelates the schedules of co-resident CTAs
 // Register budget.  Two 256-thread CTAs per SM start with 128 registers per thread; the softmax
 // warpgroup then takes kSoftmaxRegs and the other warpgroup keeps kOtherRegs.  setmaxnreg.inc can
 // only take registers that this CTA's own setmaxnreg.dec released and blocks -- with no time limit
@@ -65,10 +66,6 @@ static_assert(kSoftmaxRegs % 8 == 0 && kOtherRegs % 8 == 0 && kOtherRegs >= 24, 
 constexpr uint32_t kTmemCols = 256;    // two resident CTAs share the SM's 512 columns
 constexpr uint32_t kTmemS = 0, kTmemP = 128, kTmemO = 192;
 constexpr float kRescaleThresholdLog2 = 8.0f;
-#ifndef FA_POLY_PER_EIGHT
-#define FA_POLY_PER_EIGHT 2
-#endif
-constexpr int kPolyPerEight = FA_POLY_PER_EIGHT;  // exponentials per 8 evaluated on the FMA pipe
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait
 
 // watchdog codes (status word 0); low byte tells which wait ran out
@@ -231,7 +228,13 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       const int half_q = p.n_qtiles >> 1;
       bh = static_cast<int>(fast_div(unit, p.div_half));
       const int sidx = unit - bh * half_q;
-      qt = (n & 1) ? sidx : p.n_qtiles - 1 - sidx;
+      // CTAs that share an SM (and the grid as a whole) should not all be at the same point of
+      // their pair at the same time: half of them take the short tile of each pair first.  Which
+      // CTAs share an SM is not known; on a 148-SM B200 CTA i sits with i + 148 or with i ^ 1, and
+      // this hash separates both.  (A constant divisor: no division is executed, and nothing is
+      // kept in a register through the softmax loop, where one more live value costs spills.)
+      const int pair_swap = (blockIdx.x ^ (blockIdx.x / kSmCountHint)) & 1;
+      qt = ((n & 1) ^ pair_swap) ? sidx : p.n_qtiles - 1 - sidx;
     } else {
       if (!kPersistent && n > 0) return false;
       const int item = blockIdx.x + n * gridDim.x;
@@ -628,8 +631,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             const float p0 = ex2_approx(x0);
             const float p1 = ex2_approx(x1);
             float p2, p3;
-            if ((kPolyPerEight >= 2 && (k % 8) == 4) || (kPolyPerEight >= 4 && (k % 8) == 0) ||
-                (kPolyPerEight == 3 && (k % 16) == 8)) {
+            if ((k % 8) == 4) {   // 2 of every 8 on the FMA pipe
               exp2_poly_x2(x2, x3, p2, p3);
             } else {
               p2 = ex2_approx(x2);
