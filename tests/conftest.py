@@ -21,5 +21,18 @@ def fa_lib():
 
 
 @pytest.fixture(scope="session")
+def torch_binding(fa_lib):
+    """The compiled pybind11 / torch-extension binding, built on demand (g++ against the installed
+    torch); None where it cannot be built, so that the tests of the ctypes route still run."""
+    from tfg_flashattention_b200 import build
+    try:
+        build.build_torch_binding()
+    except Exception as e:      # no compiler, no torch headers
+        return None
+    from tfg_flashattention_b200 import _custom_flash_attn_ext
+    return _custom_flash_attn_ext
+
+
+@pytest.fixture(scope="session")
 def golden_dir():
     return os.path.join(ROOT, "tests", "golden")

@@ -15,13 +15,19 @@ MAX_ABS = 2e-2
 MEAN_ABS = 2e-3
 
 
-@pytest.fixture(scope="module")
-def cfa(fa_lib):
+@pytest.fixture(scope="module", params=["ext", "ctypes"])
+def cfa(request, fa_lib, torch_binding):
+    """The module under test, once through each binding of `forward` (the compiled torch
+    extension, as the reference ships its kernel, and the ctypes route)."""
     if not torch.cuda.is_available():
         pytest.fail("GPU tests need a CUDA device")
     from tfg_flashattention_b200 import custom_flash_attn
     assert fa_lib.fa_b200_device_ok(0) == 1, "device 0 is not compute capability 10.x"
-    return custom_flash_attn
+    if request.param == "ext" and torch_binding is None:
+        pytest.skip("the torch extension binding could not be built here")
+    assert custom_flash_attn.set_binding(request.param) == request.param
+    yield custom_flash_attn
+    custom_flash_attn.set_binding("auto")
 
 
 def _oracle():

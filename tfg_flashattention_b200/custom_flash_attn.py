@@ -24,12 +24,60 @@ is in libfa_b200.so (C ABI: include/fa_b200.h).  There is no fallback path.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
 from . import _lib
 
-__all__ = ["forward", "forward_host", "decode", "last_status", "plan"]
+__all__ = ["forward", "forward_host", "decode", "last_status", "plan", "binding", "set_binding"]
+
+# Two bindings of `forward` over the same C ABI:
+#   "ext"     the compiled pybind11 / torch extension (csrc/torch_binding.cpp, built by
+#             build.build_torch_binding()): the counterpart of the reference's torch_bind.cpp, a few
+#             microseconds of host time per call, GIL released around the launch;
+#   "ctypes"  pure Python over ctypes: needs no compiler beyond the one that built the library.
+# The extension is used when it has been built (FA_B200_BINDING=ctypes in the environment, or
+# set_binding("ctypes"), selects the other one).  Neither is a fallback for the kernel itself.
+_ext = None
+_binding = None
+
+
+def _load_ext():
+    global _ext
+    if _ext is None:
+        from . import _custom_flash_attn_ext as ext      # ImportError when it was never built
+        if ext.abi_version != _lib.ABI_VERSION:
+            raise ImportError("the torch binding was built from a different include/fa_b200.h; rebuild it "
+                              "(python -m tfg_flashattention_b200.build --binding --force)")
+        _lib.load()                                       # same checks on the library itself
+        _ext = ext
+    return _ext
+
+
+def set_binding(name: str) -> str:
+    """Select "ext", "ctypes" or "auto" (the extension when it is importable); returns the choice."""
+    global _binding
+    if name not in ("ext", "ctypes", "auto"):
+        raise ValueError("binding must be 'ext', 'ctypes' or 'auto'")
+    if name == "ctypes":
+        _binding = "ctypes"
+    else:
+        try:
+            _load_ext()
+            _binding = "ext"
+        except ImportError:
+            if name == "ext":
+                raise
+            _binding = "ctypes"
+    return _binding
+
+
+def binding() -> str:
+    """The binding `forward` goes through: "ext" or "ctypes"."""
+    if _binding is None:
+        set_binding(os.environ.get("FA_B200_BINDING", "auto"))
+    return _binding
 
 
 def _check_input(t: torch.Tensor, name: str) -> None:
@@ -95,6 +143,8 @@ def _check_qkv(Q, K, V):
 
 def forward(Q, K, V, causal=True, return_lse=False, softmax_scale=None, out=None):
     """Attention forward on the current CUDA stream of Q's device.  See the module docstring."""
+    if binding() == "ext":
+        return _ext.forward(Q, K, V, causal, return_lse, softmax_scale, out)
     _check_qkv(Q, K, V)
     B, H, N, d = Q.shape
     if out is None:
