@@ -570,6 +570,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-sweep", action="store_true", help="skip the extra configurations")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-sustained", action="store_true",
+                    help="skip the two-second sustained leg and the 200 ms minimum window (runs under a profiler)")
     ap.add_argument("--decode-case", default=None, metavar="B,H,kv_len",
                     help="time only this decode step (small runs for profilers); prints a short line")
     ap.add_argument("--ln-case", default=None, metavar="rows,cols",
@@ -647,7 +649,8 @@ def main():
     time.sleep(0.3)
     t0 = time.time()
     headline = {}
-    ms = time_kernel(cfa, q, k, v, True, args.steps, args.warmup, world, min_window_ms=200.0, detail=headline)
+    ms = time_kernel(cfa, q, k, v, True, args.steps, args.warmup, world,
+                     min_window_ms=0.0 if args.no_sustained else 200.0, detail=headline)
     t1 = time.time()
     clocks = sampler.stop(t0, t1)
     status = cfa.last_status()
@@ -657,7 +660,7 @@ def main():
     value = world * flops / (ms * 1e-3) / 1e12
     per_gpu = value / world
     # the same launch kept going for two seconds: what it holds at settled clocks and power
-    sus_ms, sus_launches, sus_clocks = time_sustained(cfa, q, k, v, 2.0, gpu_id)
+    sus_ms, sus_launches, sus_clocks = time_sustained(cfa, q, k, v, 0.02 if args.no_sustained else 2.0, gpu_id)
     sus_tf = flops / (sus_ms * 1e-3) / 1e12
     sustained = {"tflops": round(sus_tf, 1), "ms_per_launch": round(sus_ms, 5), "launches": sus_launches,
                  "seconds": round(sus_ms * sus_launches * 1e-3, 2),

@@ -73,8 +73,14 @@ def test_generate_with_cache_equals_reference_style_recompute(golden_dir):
     c = gpt2.generate(model, prompt, 5, 48, temperature=1.0, top_k=10, generator=g1)
     d = gpt2.generate(model, prompt, 5, 48, temperature=1.0, top_k=10, use_cache=False, generator=g2)
     assert torch.equal(c, d)
-    with pytest.raises(ValueError):
-        gpt2.generate(model, ids, 20, 48)
+    # past the context length the cache cannot slide: the remaining tokens are produced as the
+    # reference produces all of them, from the last context_size tokens (model_inference.py:202)
+    e = gpt2.generate(model, ids, 20, 48, temperature=0.0)                       # 40 + 20 > 48
+    f = gpt2.generate(model, ids, 20, 48, temperature=0.0, use_cache=False)
+    assert e.shape == (2, 60) and torch.equal(e, f)
+    long_prompt = torch.cat([ids, ids], dim=1)                                   # 80 > 48 from the start
+    assert torch.equal(gpt2.generate(model, long_prompt, 3, 48, temperature=0.0),
+                       gpt2.generate(model, long_prompt, 3, 48, temperature=0.0, use_cache=False))
 
 
 def test_configs_and_flops():

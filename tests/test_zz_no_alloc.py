@@ -58,6 +58,16 @@ def test_decode_static_matches_decode_on_two_calls_in_a_row(fa_lib):
         # same kernels, same chunking: equal to the bit; the suite's tolerance is the stated bound
         assert (o_new.float() - o_ref.float()).abs().max().item() <= 2e-2
         assert torch.equal(o_new, o_ref)
+        # the point of the entry point: a call allocates no device memory.  The first call on the
+        # device has done its one-time set-up; repeat it and compare the driver's count of free
+        # memory before and after (cudaMemGetInfo, not torch's caching allocator).
+        torch.cuda.synchronize(dev)
+        free_before, _ = torch.cuda.mem_get_info(dev)
+        rc = fa_lib.fa_b200_decode_static(ctypes.byref(_params(_lib, q, k, v, o_new, kv_len)))
+        torch.cuda.synchronize(dev)
+        free_after, _ = torch.cuda.mem_get_info(dev)
+        assert rc == 0 and free_after == free_before
+        assert torch.equal(o_new, o_ref)
         # and against plain torch on the first kv_len rows
         s = torch.einsum("bhd,bhnd->bhn", q.float(), k[:, :, :kv_len].float()) / 8.0
         want = torch.einsum("bhn,bhnd->bhd", torch.softmax(s, -1), v[:, :, :kv_len].float())

@@ -481,24 +481,32 @@ def generate(model, idx, max_new_tokens, context_size, temperature=1.0, top_k=No
     cuda_graph=True (with the cache, "cuda" attention) records the single-token forward once and
     replays it per token: one graph launch instead of ~15 kernel launches per layer.  Recording
     costs a few steps' time; `session=GenerationSession(model, batch, context_size)` keeps the
-    caches and the recorded step across calls."""
+    caches and the recorded step across calls.
+    The cache holds context_size rows and does not slide: once the sequence outgrows it (or if the
+    prompt alone is longer), the remaining tokens are produced the reference's way, by re-running
+    the last context_size tokens (:202), so a call that generates past the context length
+    continues exactly as it does in the reference instead of failing."""
     caches = None
     pos = 0
     step_fn = position = None
+    if use_cache and idx.shape[1] > context_size:
+        use_cache = False                  # nothing of this prompt's cache would stay valid
     if use_cache:
-        if idx.shape[1] + max_new_tokens > context_size:
-            raise ValueError("prompt + new tokens exceed the context length (the cache does not slide)")
         if session is not None:            # caches and the recorded step are reused across calls
-            if session.batch != idx.shape[0] or session.context_size < idx.shape[1] + max_new_tokens:
+            if session.batch != idx.shape[0] or session.context_size < min(context_size, idx.shape[1] + max_new_tokens):
                 raise ValueError("the generation session was made for another batch or context size")
+            context_size = min(context_size, session.context_size)
             caches, step_fn, position = session.caches, session.step_fn, session.position
         else:
             caches = model.allocate_kv_cache(idx.shape[0], context_size)
             if cuda_graph:
                 step_fn, position = model.capture_decode_step(caches)
     for step in range(max_new_tokens):
+        if use_cache and step > 0 and pos + 1 > context_size:
+            use_cache = False              # the cache is full: recompute over the sliding window from here on
         if use_cache and step > 0 and step_fn is not None:
             logits = step_fn(idx[:, -1:])
+            pos += 1
         elif use_cache:
             inp = idx if step == 0 else idx[:, -1:]
             logits = model(inp, last_token_only=True, kv_caches=caches, pos=pos)

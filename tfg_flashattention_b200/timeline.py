@@ -47,6 +47,7 @@ def main(argv: list[str]) -> None:
         raise SystemExit("build the trace library first: python -m tfg_flashattention_b200.timeline --build")
     _lib.LIB_PATH = TRACE_LIB
     from . import custom_flash_attn as cfa
+    cfa.set_binding("ctypes")      # the compiled binding is linked to the product library, not this one
     lib = _lib.load()
     B, H, N, causal = 8, 25, 4096, 0
     if argv:
