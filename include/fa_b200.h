@@ -189,9 +189,12 @@ int fa_b200_decode(const fa_b200_decode_params* p);
  * C host with a fixed memory map and no allocator to call.  This function itself calls no
  * cudaMalloc, cudaFree or other allocating routine.
  *
- *   - Problems whose scratch need (fa_b200_decode_workspace_bytes) exceeds
- *     FA_B200_STATIC_SCRATCH_BYTES are refused with FA_B200_ERR_STATIC_SCRATCH; nothing is
- *     launched.  (Up to 496 (batch, head) pairs always fit; from 592 pairs on no scratch is used.)
+ *   - The keys of a head are cut into 592 / (B * H) chunks of at least 64 rows (fa_b200_decode
+ *     cuts caches of 2048 rows and more finer than that, which this entry point does not follow,
+ *     so that what fits the buffer does not move with that tuning).  Problems whose partial
+ *     results -- 264 bytes per (batch, head) pair and chunk -- exceed FA_B200_STATIC_SCRATCH_BYTES
+ *     are refused with FA_B200_ERR_STATIC_SCRATCH; nothing is launched.  (Up to 496 (batch, head)
+ *     pairs always fit; from 592 pairs on no scratch is used.)
  *   - The first call on each device looks up the buffer's device address; make that first call
  *     outside of any stream capture.
  *   - All calls on a device share the one buffer, and it keeps whatever the previous call left in
@@ -199,7 +202,8 @@ int fa_b200_decode(const fa_b200_decode_params* p);
  *     but two calls that may run on the GPU at the same time (different streams, different host
  *     threads) race on it: serialise them, or use fa_b200_decode with separate workspaces.
  *
- * Results are identical to fa_b200_decode.  This entry point has no counterpart in the reference. */
+ * Results are identical to fa_b200_decode wherever both cut the keys into the same chunks, and
+ * equal within rounding otherwise.  This entry point has no counterpart in the reference. */
 int fa_b200_decode_static(const fa_b200_decode_params* p);
 
 /* Residual add + LayerNorm in one pass (bf16 in / out, fp32 arithmetic), for the transformer block

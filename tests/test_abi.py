@@ -67,14 +67,26 @@ def test_validate_rejects(fa_lib, mutate, code):
     p = _good_params()
     mutate(p)
     assert fa_lib.fa_b200_validate(ctypes.byref(p)) == code
-    # fa_b200_fwd applies the same checks first and makes no CUDA call when they fail
+    # fa_b200_fwd and fa_b200_fwd_plan apply the same checks first and make no CUDA call when they fail
     assert fa_lib.fa_b200_fwd(ctypes.byref(p)) == code
+    schedule, grid = ctypes.c_int32(99), ctypes.c_int32(99)
+    assert fa_lib.fa_b200_fwd_plan(ctypes.byref(p), ctypes.byref(schedule), ctypes.byref(grid)) == code
+    assert (schedule.value, grid.value) == (99, 99)            # outputs untouched on error
     assert _lib.strerror(code).startswith("fa_b200")
 
 
 def test_null_params_pointer(fa_lib):
     assert fa_lib.fa_b200_validate(None) == -1
     assert fa_lib.fa_b200_fwd(None) == -1
+    assert fa_lib.fa_b200_fwd_plan(None, None, None) == -1
+
+
+def test_plan_of_an_empty_problem_needs_no_device(fa_lib):
+    p = _good_params()
+    p.N = 0
+    schedule, grid = ctypes.c_int32(99), ctypes.c_int32(99)
+    assert fa_lib.fa_b200_fwd_plan(ctypes.byref(p), ctypes.byref(schedule), ctypes.byref(grid)) == 0
+    assert (schedule.value, grid.value) == (-1, 0)             # FA_B200_SCHEDULE_NONE, nothing to launch
 
 
 def test_strerror_covers_codes(fa_lib):
@@ -88,7 +100,7 @@ def test_decode_workspace_query_and_validation(fa_lib):
     ws = fa_lib.fa_b200_decode_workspace_bytes
     assert ws(32, 25, 1024) == 0                       # 800 heads fill the GPU: keys are not split
     assert ws(1, 25, 1024) == 0                        # few heads, short cache: one wide CTA per head
-    assert ws(1, 25, 8192) == 25 * 24 * 66 * 4         # long cache: 24 chunks per head
+    assert ws(1, 25, 8192) == 25 * 16 * 66 * 4         # long cache: 16 chunks of 512 rows per head
     assert ws(12, 25, 300) == 300 * 2 * 66 * 4         # 300 heads are too many for the wide form
     assert ws(1, 1, 100) == 0
     assert ws(1, 1, 64) == 0

@@ -17,7 +17,11 @@ import torch
 pytestmark = pytest.mark.gpu
 
 WATCHDOG_BASE = 0x10000
-WAIT_KV_FULL = 2
+# The missing K tile stalls three waits at once: the issuer's for that tile (2), and behind it the
+# producer's for the Q slot (9) and the softmax warps' for the next S (4).  They started within a
+# microsecond or two of each other, so which one runs out first -- and gets to write the word -- is
+# a matter of that microsecond; any of the three is the right report.
+EXPECTED_WAITS = {2: b"K/V tile load", 9: b"Q slot", 4: b"S = QK^T"}
 
 
 def test_wait_runs_out_is_reported_and_the_next_launch_is_correct(fa_lib):
@@ -47,8 +51,9 @@ def test_wait_runs_out_is_reported_and_the_next_launch_is_correct(fa_lib):
     assert wt.fa_b200_fwd(ctypes.byref(p)) == 0          # the launch itself succeeds
     code = wt.fa_b200_last_status(0, stream)             # synchronises: the kernel has returned
     elapsed = time.perf_counter() - t0
-    assert code == (WATCHDOG_BASE | WAIT_KV_FULL), hex(code)
-    assert b"K/V tile load ran out" in wt.fa_b200_strerror(code)
+    assert code & ~0xff == WATCHDOG_BASE and (code & 0xff) in EXPECTED_WAITS, hex(code)
+    message = wt.fa_b200_strerror(code)
+    assert b"watchdog" in message and EXPECTED_WAITS[code & 0xff] in message
     assert elapsed < 2.0, f"the kernel took {elapsed:.2f} s to give up"
     assert wt.fa_b200_last_status(0, stream) == 0        # reading the word cleared it
 

@@ -318,7 +318,15 @@ int fa_b200_fwd_plan(const fa_b200_params* p, int32_t* schedule, int32_t* grid) 
 // ------------------------------------------------------------------------------------ decode
 namespace {
 
-constexpr int kDecodeTargetCtas = 592;   // 4 CTAs per SM on a 148-SM part: enough loads in flight
+// CTAs the split aims for.  Every CTA keeps a fixed 16 KB of loads in flight, so bandwidth grows
+// with the number of resident CTAs: measured on B200 at B=8, H=25, kv_len=8192, 600 / 1800 / 2400
+// CTAs give 4.3 / 4.6 / 5.2 TB/s.  Short caches are latency-bound and pay for the second launch
+// and the partials instead (B=32, kv_len=1024: 4.8 TB/s unsplit, 4.4 split in two), so the high
+// target and its coarser chunks apply from 2048 rows on.
+constexpr int kDecodeTargetCtas = 592;        // 4 CTAs per SM on a 148-SM part
+constexpr int kDecodeTargetCtasLong = 2368;   // 16 CTAs per SM: every thread slot of the part
+constexpr int kDecodeLongLen = 2048;
+constexpr int kDecodeMinRows = 64, kDecodeMinRowsLong = 512;   // rows per chunk, at least
 
 constexpr int kDecodeWideMaxHeads = 296;   // two 1024-thread CTAs per SM on a 148-SM part
 constexpr int kDecodeWideMaxLen = 4096;    // up to 1 MB of K/V per head through one SM
@@ -326,7 +334,10 @@ constexpr int kDecodeWideMaxLen = 4096;    // up to 1 MB of K/V per head through
 // How the keys of one head are cut: `splits` chunks of `rows` rows (a multiple of the 16 lane
 // groups of a CTA).  The same rule sizes the workspace and launches the kernel.  Few heads with
 // short caches take the one-launch form instead (`wide`: one 1024-thread CTA per head, no split).
-void decode_split(int B, int H, int kv_len, int* splits, int* rows, bool* wide = nullptr) {
+// `fine_for_long` = false keeps the short-cache rule at every length: the allocation-free entry
+// point cuts that way, so that what fits its fixed scratch buffer does not depend on this tuning.
+void decode_split(int B, int H, int kv_len, int* splits, int* rows, bool* wide = nullptr,
+                  bool fine_for_long = true) {
   const long long heads = static_cast<long long>(B) * H;
   const bool w = heads <= kDecodeWideMaxHeads && kv_len <= kDecodeWideMaxLen;
   if (wide != nullptr) *wide = w;
@@ -335,8 +346,11 @@ void decode_split(int B, int H, int kv_len, int* splits, int* rows, bool* wide =
     *rows = (kv_len + 127) / 128 * 128;
     return;
   }
-  long long want = (kDecodeTargetCtas + heads - 1) / heads;
-  const long long max_splits = (kv_len + 63) / 64;            // at least 64 rows per chunk
+  const bool long_cache = fine_for_long && kv_len >= kDecodeLongLen;
+  const long long target = long_cache ? kDecodeTargetCtasLong : kDecodeTargetCtas;
+  const long long min_rows = long_cache ? kDecodeMinRowsLong : kDecodeMinRows;
+  long long want = (target + heads - 1) / heads;
+  const long long max_splits = (kv_len + min_rows - 1) / min_rows;
   if (want > max_splits) want = max_splits;
   if (want < 1) want = 1;
   long long r = (kv_len + want - 1) / want;
@@ -482,9 +496,9 @@ int fa_b200_decode_static(const fa_b200_decode_params* p) {
   if (p->B == 0 || p->H == 0) return FA_B200_OK;
   int splits = 1, rows = 0;
   bool wide = false;
-  decode_split(p->B, p->H, p->kv_len, &splits, &rows, &wide);
-  if (splits > 1 &&
-      fa_b200_decode_workspace_bytes(p->B, p->H, p->kv_len) > static_cast<int64_t>(FA_B200_STATIC_SCRATCH_BYTES))
+  decode_split(p->B, p->H, p->kv_len, &splits, &rows, &wide, /*fine_for_long=*/false);
+  if (splits > 1 && static_cast<int64_t>(p->B) * p->H * splits * fa::kDecodePartial *
+                            static_cast<int64_t>(sizeof(float)) > static_cast<int64_t>(FA_B200_STATIC_SCRATCH_BYTES))
     return FA_B200_ERR_STATIC_SCRATCH;
 
   DeviceGuard guard(p->device);
