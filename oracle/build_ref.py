@@ -1,6 +1,7 @@
 """Compile the reference project's own CUDA attention kernel into oracle/_ref/libref_v1.so.
 
-    python oracle/build_ref.py [/path/to/reference]        (default: /root/reference)
+    python oracle/build_ref.py [/path/to/reference]
+    (default: $FA_REFERENCE_ROOT, else the folder `reference` next to this repository)
 
 TEST / BENCHMARK INFRASTRUCTURE ONLY.  The reference's translation unit src/cpp/v1.cu (launcher,
 :4-42) with its header src/cpp/headers/v1_implementation.hpp (kernel, :7-171) is compiled from
@@ -22,10 +23,12 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
 LIB_PATH = os.path.join(OUT_DIR, "libref_v1.so")
+DEFAULT_REF_ROOT = os.environ.get("FA_REFERENCE_ROOT") or os.path.normpath(os.path.join(HERE, "..", "..", "reference"))
 
 
-def build(ref_root: str = "/root/reference", force: bool = False) -> str | None:
+def build(ref_root: str | None = None, force: bool = False) -> str | None:
     """Returns the library path, or None when the reference sources are not available."""
+    ref_root = ref_root or DEFAULT_REF_ROOT
     src = os.path.join(ref_root, "src", "cpp", "v1.cu")
     inc = os.path.join(ref_root, "src", "cpp", "headers")
     if not os.path.isfile(src):
@@ -46,4 +49,4 @@ def build(ref_root: str = "/root/reference", force: bool = False) -> str | None:
 
 
 if __name__ == "__main__":
-    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", force=True))
+    print(build(sys.argv[1] if len(sys.argv) > 1 else None, force=True))

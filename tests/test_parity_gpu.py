@@ -359,3 +359,37 @@ def test_non_default_stream(cfa):
         o = cfa.forward(q, k, v)
         assert cfa.last_status() == 0
     assert torch.equal(o, ref)
+
+
+def test_calls_from_two_host_threads(cfa):
+    """The library is re-entrant per device (the reference's binding holds the GIL through its
+    launch, torch_bind.cpp:21-45; the compiled binding here releases it): two host threads, each
+    on its own stream and its own tensors, interleave their launches; every result equals the
+    single-threaded one bit for bit.  Also exercises the per-thread tensor-map cache."""
+    import threading
+    torch.manual_seed(51)
+    problems = [tuple(torch.randn(2, 3, n, 64, device="cuda").bfloat16() for _ in range(3)) for n in (200, 513)]
+    want = [cfa.forward(*p) for p in problems]
+    assert cfa.last_status() == 0
+    torch.cuda.synchronize()
+    errors = []
+
+    def worker(i):
+        try:
+            s = torch.cuda.Stream()
+            with torch.cuda.stream(s):
+                for _ in range(50):
+                    got = cfa.forward(*problems[i])
+                s.synchronize()
+                if not torch.equal(got, want[i]):
+                    errors.append(f"thread {i}: result differs")
+        except Exception as e:       # surfaced in the main thread below
+            errors.append(f"thread {i}: {e!r}")
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    assert cfa.last_status() == 0
