@@ -81,6 +81,28 @@ enum WaitId : uint32_t {
   kWaitOFull = 6, kWaitDrain = 7, kWaitSFree = 8, kWaitQEmpty = 9, kWaitOFree = 10
 };
 
+// Optional timeline trace (compile with -DFA_TRACE; timeline.py builds that variant into a library
+// of its own): lane 0 of softmax warps 0 and 3 and of the issuer warp store clock64() stamps of
+// their hand-offs for the CTA's first kTraceTilesSm tiles.  The stamps go to shared memory -- a
+// store to global memory inside the loop would sit in front of every mbarrier arrive (release
+// semantics) and stretch the very phases that are measured -- and the CTA named by
+// g_fa_trace_block copies them out when it ends.  The product library is built without it and
+// carries none of this.
+#ifdef FA_TRACE
+constexpr int kTraceRoles = 4, kTraceTiles = 64, kTraceEvents = 16;   // layout of the global copy
+constexpr int kTraceRolesSm = 3, kTraceTilesSm = 32, kTraceEventsSm = 10;
+constexpr int kTraceSlots = kTraceRoles * kTraceTiles * kTraceEvents;
+__device__ unsigned long long g_fa_trace[kTraceSlots];
+__device__ int g_fa_trace_block = 0;
+#define FA_TRACE_EVENT(role, g, e)                                                     \
+  do {                                                                                 \
+    if ((role) >= 0 && (threadIdx.x & 31) == 0 && (g) < kTraceTilesSm)                 \
+      sm.trace[role][g][e] = clock64();                                                \
+  } while (0)
+#else
+#define FA_TRACE_EVENT(role, g, e) do {} while (0)
+#endif
+
 struct __align__(1024) SharedStorage {
   uint8_t q[kTileBytes];
   uint8_t kv[kKVSlots][kTileBytes];
@@ -97,6 +119,9 @@ struct __align__(1024) SharedStorage {
   uint32_t tmem_base;
   uint32_t abort;
   float2 owed[kBlockM];          // per row of a finished item: {1 / l, m * c + log2 l} for its epilogue
+#ifdef FA_TRACE
+  unsigned long long trace[kTraceRolesSm][kTraceTilesSm][kTraceEventsSm];
+#endif
 };
 constexpr int kSmemBytes = sizeof(SharedStorage) + 1024;  // + slack to align the base to 1024
 static_assert(kCtasPerSm * (kSmemBytes + 1024) <= 227 * 1024, "two CTAs must fit in one SM");
@@ -138,25 +163,6 @@ struct FwdParams {
   float scale_log2;           // softmax_scale * log2(e)
   unsigned int* status;       // [4] watchdog words in global memory
 };
-
-// Optional timeline trace (compile with -DFA_TRACE; timeline.py builds that variant into a library
-// of its own): lane 0 of softmax warps 0 and 3 and of the issuer warp of the CTA named by
-// g_fa_trace_block store clock64() stamps of their hand-offs for the first 64 tiles.  The product
-// library is built without it and carries none of this.
-#ifdef FA_TRACE
-constexpr int kTraceRoles = 4, kTraceTiles = 64, kTraceEvents = 16;
-constexpr int kTraceSlots = kTraceRoles * kTraceTiles * kTraceEvents;
-__device__ unsigned long long g_fa_trace[kTraceSlots];
-__device__ int g_fa_trace_block = 0;
-#define FA_TRACE_EVENT(role, g, e)                                                     \
-  do {                                                                                 \
-    if ((role) >= 0 && (threadIdx.x & 31) == 0 && blockIdx.x == g_fa_trace_block &&    \
-        (g) < kTraceTiles)                                                             \
-      g_fa_trace[((role) * kTraceTiles + (g)) * kTraceEvents + (e)] = clock64();       \
-  } while (0)
-#else
-#define FA_TRACE_EVENT(role, g, e) do {} while (0)
-#endif
 
 struct Watch {
   volatile uint32_t* abort;
@@ -281,6 +287,10 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     sm.abort = 0;
     fence_mbar_init();
   }
+#ifdef FA_TRACE
+  for (int i = threadIdx.x; i < kTraceRolesSm * kTraceTilesSm * kTraceEventsSm; i += kNumThreads)
+    (&sm.trace[0][0][0])[i] = 0ull;
+#endif
   if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(&sm.tmem_base), kTmemCols);
     tmem_relinquish();
@@ -697,6 +707,16 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+#ifdef FA_TRACE
+  if (blockIdx.x == g_fa_trace_block) {
+    for (int i = threadIdx.x; i < kTraceRolesSm * kTraceTilesSm * kTraceEventsSm; i += kNumThreads) {
+      const int role = i / (kTraceTilesSm * kTraceEventsSm);
+      const int g = (i / kTraceEventsSm) % kTraceTilesSm;
+      const int e = i % kTraceEventsSm;
+      g_fa_trace[(role * kTraceTiles + g) * kTraceEvents + e] = sm.trace[role][g][e];
+    }
+  }
+#endif
 }
 
 }  // namespace fa
