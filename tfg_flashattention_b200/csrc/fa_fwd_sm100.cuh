@@ -119,6 +119,7 @@ struct __align__(1024) SharedStorage {
   uint32_t tmem_base;
   uint32_t abort;
   float2 owed[kBlockM];          // per row of a finished item: {1 / l, m * c + log2 l} for its epilogue
+  int4 owed_at[2][kBlockM];      // per row, item n in slot n & 1: {first query row, head, batch} of the item
 #ifdef FA_TRACE
   unsigned long long trace[kTraceRolesSm][kTraceTilesSm][kTraceEventsSm];
 #endif
@@ -475,18 +476,25 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     // first tile (after that tile's P is stored, before the issuer is told about it): by then the
     // last O += P V of the finished item has long completed, so nobody sits waiting for it.
     // What the epilogue needs of the finished item waits in shared memory, not in registers that
-    // would stay live through the hot loop: each thread parks its row's {1 / l, m * c + log2 l},
-    // and the item itself is decoded again from its index.
+    // would stay live through the hot loop: each thread parks its row's {1 / l, m * c + log2 l}
+    // when the item ends and the item's coordinates when it starts (decoding the item again from
+    // its index cost the epilogue ~170 clocks of dependent integer arithmetic).
     // O / l -> bf16 -> swizzled staging tile -> TMA store; LSE.  Reads O of the owed item.
     auto epilogue = [&](const int owed_n) -> bool {
-      Item ow;
-      get_item(owed_n, ow);
+      int4 at;
+      if (kPersistent) {
+        at = sm.owed_at[owed_n & 1][r];
+      } else {             // one item per CTA: nothing is in a hurry after its last tile
+        Item ow;
+        get_item(owed_n, ow);
+        at = make_int4(ow.q_row, ow.h, ow.b, 0);
+      }
       const float2 parked = sm.owed[r];
       const uint32_t bar_o_free = smem_u32(&sm.o_free);
       // this thread's row of the staging tile; 16-byte chunk c goes to position c ^ (r & 7)
       // (the 128-byte swizzle the TMA store expects)
       const uint32_t stage_row = smem_u32(sm.o_stage) + r * 128;
-      const int owed_q_row = ow.q_row, owed_h = ow.h, owed_b = ow.b;
+      const int owed_q_row = at.x, owed_h = at.y, owed_b = at.z;
       tc_fence_after();
       // O / l -> bf16 while loading, 32 columns at a time (keeps the register peak low: the
       // persistent kernel runs this in the middle of a tile)
@@ -536,6 +544,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     for (; ok; ++n) {
       Item w;
       if (!get_item(n, w)) break;
+      if (kPersistent) sm.owed_at[n & 1][r] = make_int4(w.q_row, w.h, w.b, 0);   // read back by this same thread
       float m_ref = -CUDART_INF_F;  // max the exponentials are currently taken against (raw scores)
       float l = 0.f;                // running sum of exp2((s - m_ref) * c)
 
