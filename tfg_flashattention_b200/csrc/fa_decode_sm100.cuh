@@ -20,16 +20,10 @@
 
 namespace fa {
 
-#ifndef FA_DECODE_THREADS
-#define FA_DECODE_THREADS 128
-#endif
-#ifndef FA_DECODE_UNROLL
-#define FA_DECODE_UNROLL 4
-#endif
-constexpr int kDecodeThreads = FA_DECODE_THREADS;   // a warp's 32 lanes = 4 groups of 8 lanes
+constexpr int kDecodeThreads = 128;          // a warp's 32 lanes = 4 groups of 8 lanes
 constexpr int kDecodeGroups = kDecodeThreads / 8;   // 16 lane groups, each owns whole rows
 constexpr int kDecodeWideThreads = 1024;            // the one-CTA-per-head form for few heads
-constexpr int kDecodeUnroll = FA_DECODE_UNROLL;     // rows in flight per lane group
+constexpr int kDecodeUnroll = 4;             // rows in flight per lane group (8: 3.3-4.0 TB/s against 4.3-5.2)
 constexpr int kDecodePartial = 66;           // floats per partial: m, l, o[64]
 
 struct DecodeParams {
