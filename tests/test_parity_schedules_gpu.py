@@ -125,6 +125,37 @@ def test_persistent_rotated_causal_schedule(cfa, B, H, N):
         assert torch.equal(alone[0, 0], o[b, h])
 
 
+@pytest.mark.parametrize("causal,N", [(True, 256), (False, 128), (True, 128)])
+def test_many_items_per_cta(cfa, causal, N):
+    """A persistent CTA decodes all its work items into a table of 256 entries when it starts.
+    Here every CTA gets about 250 of them (generated on the device: 1-2 GB of inputs); sampled
+    heads from the first to the last are compared with the oracle and with the same head computed
+    alone.  One more batch entry per CTA than the table holds and the launcher takes one CTA per
+    tile instead."""
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    per_cta = 250
+    tiles = N // 128
+    heads = (2 * sms * per_cta) // tiles          # items = heads * tiles = 2 * sms * per_cta
+    B, H = heads // 8, 8
+    g = torch.Generator(device="cuda").manual_seed(9100 + N + int(causal))
+    qb, kb, vb = (torch.randn(B, H, N, 64, device="cuda", generator=g).bfloat16() for _ in range(3))
+    want = {(True, 256): "persistent_paired", (True, 128): "persistent_rotated", (False, 128): "persistent_full"}
+    assert cfa.plan(qb, kb, vb, causal=causal) == (want[(causal, N)], 2 * sms)
+    o, lse = cfa.forward(qb, kb, vb, causal=causal, return_lse=True)
+    assert cfa.last_status() == 0
+    assert torch.isfinite(o).all() and torch.isfinite(lse).all()
+    picked = _spread_heads(B, H, 12)
+    _check_heads_fully(o, lse, qb, kb, vb, picked, causal)
+    for (b, h) in picked[::3]:
+        alone, alone_lse = cfa.forward(qb[b:b + 1, h:h + 1], kb[b:b + 1, h:h + 1], vb[b:b + 1, h:h + 1],
+                                       causal=causal, return_lse=True)
+        assert torch.equal(alone[0, 0], o[b, h]) and torch.equal(alone_lse[0, 0], lse[b, h])
+    # past the table: 2 * sms * 256 items fit, a few more do not
+    big_b = (2 * sms * 256) // (tiles * H) + 2
+    t = torch.empty(big_b, H, N, 64, device="cuda", dtype=torch.bfloat16)
+    assert cfa.plan(t, t, t, causal=causal) == ("cta_per_tile", big_b * H * tiles)
+
+
 def test_plan_reports_each_schedule(cfa):
     """The dispatch rule itself, on shapes of the benchmark configurations."""
     def plan(B, H, N, causal):

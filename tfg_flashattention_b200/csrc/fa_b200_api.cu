@@ -202,7 +202,13 @@ FwdPlan plan_fwd(const fa_b200_params* p, const DeviceState& st) {
   pl.persistent = can_pair ? kv_tiles <= 16
                            : (pl.items >= 2LL * st.resident_ctas && kv_tiles <= 8);
   pl.paired = pl.persistent && can_pair;
-  const long long work_units = pl.paired ? pl.items / 2 : pl.items;
+  long long work_units = pl.paired ? pl.items / 2 : pl.items;
+  // a persistent CTA keeps its items in a table of fa::kItemTable entries
+  if (pl.persistent && (work_units + st.resident_ctas - 1) / st.resident_ctas * (pl.paired ? 2 : 1) >
+                           fa::kItemTable) {
+    pl.persistent = pl.paired = false;
+    work_units = pl.items;
+  }
   pl.grid = static_cast<unsigned>(
       pl.persistent ? (work_units > st.resident_ctas ? st.resident_ctas : work_units) : pl.items);
   return pl;

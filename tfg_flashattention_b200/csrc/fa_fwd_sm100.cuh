@@ -66,6 +66,8 @@ static_assert(kSoftmaxRegs % 8 == 0 && kOtherRegs % 8 == 0 && kOtherRegs >= 24, 
 constexpr uint32_t kTmemCols = 256;    // two resident CTAs share the SM's 512 columns
 constexpr uint32_t kTmemS = 0, kTmemP = 128, kTmemO = 192;
 constexpr float kRescaleThresholdLog2 = 8.0f;
+constexpr int kItemTable = 256;        // work items per CTA decoded ahead (one per thread at start-up)
+static_assert(kItemTable == kNumThreads, "one table entry per thread");
 #ifdef FA_WAIT_TEST
 // Test build (build.build_wait_test_library): waits give up after 2 ms, and the producer leaves out
 // one K tile (see load_kv), so that a test can watch a bounded wait run out and the kernel drain.
@@ -119,7 +121,8 @@ struct __align__(1024) SharedStorage {
   uint32_t tmem_base;
   uint32_t abort;
   float2 owed[kBlockM];          // per row of a finished item: {1 / l, m * c + log2 l} for its epilogue
-  int4 owed_at[2][kBlockM];      // per row, item n in slot n & 1: {first query row, head, batch} of the item
+  int4 items[kItemTable];        // persistent kernel: this CTA's first work items, decoded once:
+                                 // {first query row, K/V tiles (0 = no such item), head, batch}
 #ifdef FA_TRACE
   unsigned long long trace[kTraceRolesSm][kTraceTilesSm][kTraceEventsSm];
 #endif
@@ -192,7 +195,7 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, const Wa
   }
   return false;
 }
-// The same for a whole converged warp: every lane polls, the verdict is made uniform.
+// The same for a whole converged warp: every lane polls, the answer is made uniform.
 __device__ __forceinline__ bool wait_bar_warp(uint32_t bar, uint32_t parity, const Watch& w,
                                               uint32_t id) {
   return __all_sync(0xffffffffu, wait_bar(bar, parity, w, id));
@@ -233,7 +236,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
   //   persistent, rotated   (odd tile count, or non-causal) stride through single items, the tile
   //                         order inside a head rotated by the head index.
   struct Item { int b, h, q_row, ns; };
-  auto get_item = [&](int n, Item& w) -> bool {
+  auto decode_item = [&](int n, Item& w) -> bool {
     int bh, qt;
     if (kPersistent && kCausal && p.paired) {
       const int unit = blockIdx.x + (n >> 1) * gridDim.x;
@@ -271,6 +274,20 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     w.ns = kCausal ? min(nkv, qt + 1) : nkv;   // K/V tiles this query tile attends to
     return true;
   };
+  // Decoding costs ~170 clocks of dependent integer arithmetic, and every role would pay it on
+  // the path between two work items.  A persistent CTA therefore decodes all its items once, one
+  // per thread, before the start-up barrier; afterwards an item is one shared-memory load (the
+  // same address for the whole warp).  The launcher picks a persistent schedule only where a CTA
+  // gets at most kItemTable items.
+  auto get_item = [&](int n, Item& w) -> bool {
+    if (kPersistent) {
+      if (n >= kItemTable) return false;
+      const int4 e = sm.items[n];
+      w.q_row = e.x; w.ns = e.y; w.h = e.z; w.b = e.w;
+      return e.y != 0;
+    }
+    return decode_item(n, w);
+  };
 
   // ---- one-time setup
   if (threadIdx.x == 0) {
@@ -295,6 +312,11 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
   if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(&sm.tmem_base), kTmemCols);
     tmem_relinquish();
+  }
+  if (kPersistent) {
+    Item t;
+    const bool has = decode_item(threadIdx.x, t);
+    sm.items[threadIdx.x] = has ? make_int4(t.q_row, t.ns, t.h, t.b) : make_int4(0, 0, 0, 0);
   }
   tc_fence_before();
   __syncthreads();
@@ -477,24 +499,17 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     // last O += P V of the finished item has long completed, so nobody sits waiting for it.
     // What the epilogue needs of the finished item waits in shared memory, not in registers that
     // would stay live through the hot loop: each thread parks its row's {1 / l, m * c + log2 l}
-    // when the item ends and the item's coordinates when it starts (decoding the item again from
-    // its index cost the epilogue ~170 clocks of dependent integer arithmetic).
+    // when the item ends, and the item's coordinates come from the item table again.
     // O / l -> bf16 -> swizzled staging tile -> TMA store; LSE.  Reads O of the owed item.
     auto epilogue = [&](const int owed_n) -> bool {
-      int4 at;
-      if (kPersistent) {
-        at = sm.owed_at[owed_n & 1][r];
-      } else {             // one item per CTA: nothing is in a hurry after its last tile
-        Item ow;
-        get_item(owed_n, ow);
-        at = make_int4(ow.q_row, ow.h, ow.b, 0);
-      }
+      Item ow;
+      get_item(owed_n, ow);
       const float2 parked = sm.owed[r];
       const uint32_t bar_o_free = smem_u32(&sm.o_free);
       // this thread's row of the staging tile; 16-byte chunk c goes to position c ^ (r & 7)
       // (the 128-byte swizzle the TMA store expects)
       const uint32_t stage_row = smem_u32(sm.o_stage) + r * 128;
-      const int owed_q_row = at.x, owed_h = at.y, owed_b = at.z;
+      const int owed_q_row = ow.q_row, owed_h = ow.h, owed_b = ow.b;
       tc_fence_after();
       // O / l -> bf16 while loading, 32 columns at a time (keeps the register peak low: the
       // persistent kernel runs this in the middle of a tile)
@@ -544,7 +559,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     for (; ok; ++n) {
       Item w;
       if (!get_item(n, w)) break;
-      if (kPersistent) sm.owed_at[n & 1][r] = make_int4(w.q_row, w.h, w.b, 0);   // read back by this same thread
       float m_ref = -CUDART_INF_F;  // max the exponentials are currently taken against (raw scores)
       float l = 0.f;                // running sum of exp2((s - m_ref) * c)
 
