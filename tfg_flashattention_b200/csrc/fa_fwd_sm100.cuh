@@ -695,18 +695,20 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         tmem_wait_st();
         FA_TRACE_EVENT(trole, g, 6);
 
-        // the epilogue owed to the previous item: its O is final (the wait above covered its last
-        // PV) and must be read before the issuer accumulates this item's first P V into O
-        if (kPersistent && j == 0 && n > 0) {
-          ok = epilogue(n - 1);
-          if (!ok) break;
-        }
-
         FA_TRACE_EVENT(trole, g, 7);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_p);
         FA_TRACE_EVENT(trole, g, 8);
+
+        // The epilogue owed to the previous item: its O is final (the o_full wait above covered
+        // its last PV).  It runs behind the hand-off of this item's first P: the issuer holds the
+        // PV that overwrites O until the epilogue has read it (o_free), and at the end of the
+        // tile body the test costs the ordinary tiles no jump over the inlined code.
+        if (kPersistent && j == 0 && n > 0) {
+          ok = epilogue(n - 1);
+          if (!ok) break;
+        }
       }
       if (!ok) break;
       // (approximate reciprocal and logarithm: 1 ulp and 2^-22 absolute, far inside the bf16

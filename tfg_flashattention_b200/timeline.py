@@ -32,8 +32,10 @@ def build_trace_library() -> str:
 
 SOFTMAX_PHASES = [  # (label, from event, to event)
     ("wait_S", 0, 1), ("ld_S", 1, 2), ("mask+max", 2, 3), ("wait_O", 3, 4), ("exp+stP", 4, 5),
-    ("wait_st", 5, 6), ("epilogue", 6, 7), ("arrive", 7, 8),
+    ("wait_st", 5, 6), ("arrive", 6, 8),
 ]
+# "tail" = from the arrive to the next tile's start: the loop's way back and, on the first tile of
+# an item, the epilogue owed to the previous item
 
 
 def main(argv: list[str]) -> None:
@@ -67,18 +69,18 @@ def main(argv: list[str]) -> None:
     t = np.array(buf[:], dtype=np.int64).reshape(4, 64, 16)
     for role, name in ((0, "softmax warp 0"), (1, "softmax warp 3")):
         print(f"## {name}: clocks per phase; ITEM marks the first tile of a work item")
-        print("  g      " + " ".join(f"{lab:>9s}" for lab, _, _ in SOFTMAX_PHASES) + "    period")
-        prev = None
+        print("  g      " + " ".join(f"{lab:>9s}" for lab, _, _ in SOFTMAX_PHASES) + "      tail    period")
         rows = []
         for g in range(64):
             a = t[role, g]
             if a[0] == 0:
                 break
             d = [int(a[e1] - a[e0]) if a[e0] and a[e1] else 0 for _, e0, e1 in SOFTMAX_PHASES]
-            period = int(a[0] - prev) if prev is not None else 0
-            prev = a[0]
-            rows.append(d + [period])
-            print(f" {g:2d} {'ITEM' if a[9] else '    '} " + " ".join(f"{x:9d}" for x in d) + f" {period:9d}")
+            nxt = int(t[role, g + 1, 0]) if g + 1 < 64 else 0
+            tail = nxt - int(a[8]) if nxt and a[8] else 0
+            period = nxt - int(a[0]) if nxt else 0
+            rows.append(d + [tail, period])
+            print(f" {g:2d} {'ITEM' if a[9] else '    '} " + " ".join(f"{x:9d}" for x in d) + f" {tail:9d} {period:9d}")
         if len(rows) > 4:
             body = np.array(rows[2:-1])
             print("  median " + " ".join(f"{int(x):9d}" for x in np.median(body, axis=0)))
