@@ -119,7 +119,8 @@ struct __align__(1024) SharedStorage {
   uint64_t o_full;               // O += P V_j finished (P reusable, O stable)
   uint64_t o_free;               // the epilogue has read O: the next item may overwrite it
   uint32_t tmem_base;
-  uint32_t abort;
+  uint32_t abort;                // 0, or the watchdog code of the first wait that gave up
+  uint32_t abort_who;            // thread index | parity << 16 of that wait
   float2 owed[kBlockM];          // per row of a finished item: {1 / l, m * c + log2 l} for its epilogue
   int4 items[kItemTable];        // persistent kernel: this CTA's first work items, decoded once:
                                  // {first query row, K/V tiles (0 = no such item), head, batch}
@@ -169,29 +170,34 @@ struct FwdParams {
 };
 
 struct Watch {
-  volatile uint32_t* abort;
-  unsigned int* status;
+  volatile uint32_t* abort;   // shared memory: 0, or the code of the first wait that gave up
+  volatile uint32_t* who;     // shared memory: thread index | parity << 16 of that wait
 };
 
+// A bounded wait.  Each failed try_wait suspends the thread for a while in hardware; every 64 of
+// them the loop looks at the CTA's abort word and at the clock.  A wait that runs out of time
+// leaves its code in shared memory and returns false; the kernel's teardown copies the first
+// such code to the status words in global memory.  (Kept this small on purpose: the function is
+// inlined at fourteen places, and the tile loop lives off the instruction cache -- the earlier
+// form with the status words written at every site cost 1-2 % through its size alone.)
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, const Watch& w,
                                          uint32_t id, uint64_t limit_ns = kWaitLimitNs,
                                          bool heed_abort = true) {
+  static_assert(kWaitLimitNs < 4000000000ull, "the 32-bit timer difference would wrap");
+  uint32_t t0 = 0;   // the low word of the nanosecond timer is enough: limits are below 4 s
 #pragma unroll 1
-  for (int quick = 0; quick < 16; ++quick)
+  for (uint32_t polls = 0; polls < (1u << 26); ++polls) {
     if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
-  for (uint32_t polls = 1; polls < (1u << 26); ++polls) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((polls & 63u) == 0u) {
+    if ((polls & 63u) == 63u) {
       if (heed_abort && *w.abort) return false;
-      if (globaltimer_ns() - t0 > limit_ns) break;
+      const uint32_t now = globaltimer_lo_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > static_cast<uint32_t>(limit_ns)) break;
     }
   }
-  *w.abort = 1;
-  if (atomicCAS(w.status, 0u, kWatchdogBase | id) == 0u) {
-    w.status[1] = blockIdx.x;
-    w.status[2] = threadIdx.x;
-    w.status[3] = parity;
+  if (*w.abort == 0) {
+    *w.who = threadIdx.x | (parity << 16);
+    *w.abort = kWatchdogBase | id;
   }
   return false;
 }
@@ -303,6 +309,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       mbar_init(smem_u32(&sm.kv_empty[i]), 1);
     }
     sm.abort = 0;
+    sm.abort_who = 0;
     fence_mbar_init();
   }
 #ifdef FA_TRACE
@@ -322,7 +329,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = sm.tmem_base;
-  const Watch watch{&sm.abort, p.status};
+  const Watch watch{&sm.abort, &sm.abort_who};
 
   auto slot_of = [](int it) { return it % kKVSlots; };
   auto par_of = [](int it) { return static_cast<uint32_t>((it / kKVSlots) & 1); };
@@ -731,6 +738,13 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
   if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && sm.abort != 0) {   // a wait gave up: the first CTA to say so is recorded
+    if (atomicCAS(p.status, 0u, sm.abort) == 0u) {
+      p.status[1] = blockIdx.x;
+      p.status[2] = sm.abort_who & 0xffffu;
+      p.status[3] = sm.abort_who >> 16;
+    }
   }
 #ifdef FA_TRACE
   if (blockIdx.x == g_fa_trace_block) {

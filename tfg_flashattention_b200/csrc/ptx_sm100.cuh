@@ -11,9 +11,9 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
-__device__ __forceinline__ uint64_t globaltimer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+__device__ __forceinline__ uint32_t globaltimer_lo_ns() {
+  uint32_t t;
+  asm volatile("mov.u32 %0, %globaltimer_lo;" : "=r"(t));
   return t;
 }
 
