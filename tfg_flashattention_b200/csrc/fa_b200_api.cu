@@ -78,9 +78,11 @@ void init_device(int dev) {
   // The kernel moves registers between its warpgroups with setmaxnreg; that only works (and
   // otherwise blocks for ever) if the compiler gave the kernel the launch allocation the budget
   // in fa_fwd_sm100.cuh assumes.  Refuse to launch a build where it did not.
-  const void* variants[4] = {reinterpret_cast<const void*>(&fa::fa_fwd_kernel<false, false>),
+  const void* variants[6] = {reinterpret_cast<const void*>(&fa::fa_fwd_kernel<false, false>),
+                             reinterpret_cast<const void*>(&fa::fa_fwd_kernel<false, false, true>),
                              reinterpret_cast<const void*>(&fa::fa_fwd_kernel<false, true>),
                              reinterpret_cast<const void*>(&fa::fa_fwd_kernel<true, false>),
+                             reinterpret_cast<const void*>(&fa::fa_fwd_kernel<true, false, true>),
                              reinterpret_cast<const void*>(&fa::fa_fwd_kernel<true, true>)};
   for (const void* fn : variants) {
     cudaFuncAttributes fattr;
@@ -289,11 +291,14 @@ int fa_b200_fwd(const fa_b200_params* p) {
   kp.n_units = static_cast<int>(pl.items / 2);
   kp.div_half = fa::make_fast_div(static_cast<uint32_t>(kp.n_qtiles > 1 ? kp.n_qtiles / 2 : 1));
   const cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+  const bool ragged = (p->N % fa::kBlockN) != 0;   // non-causal only: the causal mask covers the columns past N
   if (pl.persistent) {
     if (kp.causal) fa::fa_fwd_kernel<true, true><<<pl.grid, fa::kNumThreads, fa::kSmemBytes, stream>>>(mq, mk, mv, mo, kp);
+    else if (ragged) fa::fa_fwd_kernel<true, false, true><<<pl.grid, fa::kNumThreads, fa::kSmemBytes, stream>>>(mq, mk, mv, mo, kp);
     else fa::fa_fwd_kernel<true, false><<<pl.grid, fa::kNumThreads, fa::kSmemBytes, stream>>>(mq, mk, mv, mo, kp);
   } else {
     if (kp.causal) fa::fa_fwd_kernel<false, true><<<pl.grid, fa::kNumThreads, fa::kSmemBytes, stream>>>(mq, mk, mv, mo, kp);
+    else if (ragged) fa::fa_fwd_kernel<false, false, true><<<pl.grid, fa::kNumThreads, fa::kSmemBytes, stream>>>(mq, mk, mv, mo, kp);
     else fa::fa_fwd_kernel<false, false><<<pl.grid, fa::kNumThreads, fa::kSmemBytes, stream>>>(mq, mk, mv, mo, kp);
   }
   return static_cast<int>(cudaGetLastError());

@@ -218,7 +218,10 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // sequences and for grids too small to balance statically).
 // kCausal selects the masking code at compile time (the non-causal instantiation carries none of
 // the diagonal-tile handling).
-template <bool kPersistent, bool kCausal>
+// kRagged (non-causal only): N is not a multiple of 128, the last K/V tile of every item needs its
+// columns past N masked.  The 128 tests for that sit inside the tile loop, and the loop's speed
+// depends on its code size, so sequences of whole tiles get an instantiation without them.
+template <bool kPersistent, bool kCausal, bool kRagged = false>
 __global__ void __launch_bounds__(kNumThreads, kCtasPerSm)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
               const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
@@ -611,7 +614,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
               }
             }
           }
-        } else if (col0 + kBlockN > p.N) {  // ragged last tile: TMA zero-fill gives score 0, not -inf
+        } else if (kRagged && col0 + kBlockN > p.N) {  // ragged last tile: TMA zero-fill gives score 0, not -inf
           const int lim = p.N - col0;
 #pragma unroll
           for (int k = 0; k < kBlockN; ++k)
